@@ -2,7 +2,8 @@
 
 One tensor per page group holds the keys and values of all its caches:
 ``[caches, 2 (K, V), pages, kv_heads, page_size, head_dim]`` in the activation dtype, so that one
-(page, head) tile of K or V is contiguous.  The reference stores token-major rows
+(page, head) tile of K or V is contiguous (where values have a size of their own, K and V are two tensors
+``[caches, pages, kv_heads, page_size, head_dim | v_dim]``).  The reference stores token-major rows
 ``[n_embd_gqa, n_cells]`` per layer (src/iian/kv_cache.cpp:163-164); the cell numbering
 (page * page_size + offset, include/iian/kv_cache.h:135-137) is the same.
 
@@ -54,7 +55,8 @@ def plan_groups(needs: Dict[int, object], capacity_tokens: int, block_size: int,
     for need, cids in by_need.items():
         tokens = capacity_tokens if need.window is None or window_tokens is None else min(capacity_tokens, window_tokens)
         n_blocks = max(1, (tokens + block_size - 1) // block_size)
-        name = (f"kv{need.num_kv_heads}x{need.head_dim}" if isinstance(need, KVNeed) else f"row{need.width}") \
+        name = (f"kv{need.num_kv_heads}x{need.head_dim}" + (f"v{need.v_dim}" if need.v_dim is not None else "")
+                if isinstance(need, KVNeed) else f"row{need.width}") \
             + (f"w{need.window}" if need.window else "")
         groups.append(PageGroup(name=name, cache_ids=tuple(cids), window=need.window, num_blocks=n_blocks))
         kinds.append(need)
@@ -79,6 +81,16 @@ class CacheStorage:
                 self.bytes += t.numel() * t.element_size()
                 for i, cid in enumerate(grp.cache_ids):
                     self._views[cid] = RowView(group=g, rows=t[i])
+                continue
+            if need.value_dim != need.head_dim:
+                tk = torch.zeros((len(grp.cache_ids), grp.num_blocks, need.num_kv_heads, block_size, need.head_dim),
+                                 dtype=dtype, device=device)
+                tv = torch.zeros((len(grp.cache_ids), grp.num_blocks, need.num_kv_heads, block_size, need.value_dim),
+                                 dtype=dtype, device=device)
+                self.kv += [tk, tv]
+                self.bytes += (tk.numel() + tv.numel()) * tk.element_size()
+                for i, cid in enumerate(grp.cache_ids):
+                    self._views[cid] = KVView(group=g, k=tk[i], v=tv[i])
                 continue
             t = torch.zeros((len(grp.cache_ids), 2, grp.num_blocks, need.num_kv_heads, block_size, need.head_dim),
                             dtype=dtype, device=device)

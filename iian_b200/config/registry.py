@@ -30,6 +30,12 @@ class Architecture:
     """
 
     name: str = ""
+    # True: some sizes are given by the shapes of the weight file's tensors only; ``with_tensor_sizes(raw, shapes)`` then
+    # returns ``raw`` completed with them before ``load_config`` sees it (``load_model_config``)
+    reads_tensor_shapes: bool = False
+
+    def with_tensor_sizes(self, raw: Mapping[str, Any], shapes: Mapping[str, tuple]) -> Mapping[str, Any]:
+        return raw
 
     def load_config(self, raw: Mapping[str, Any]):  # pragma: no cover - interface
         raise NotImplementedError
@@ -75,7 +81,7 @@ def get_architecture(name: str) -> Architecture:
 
 def _load_builtin() -> None:
     # importing the module registers the plug-in
-    from ..models import galodra, lekilix, qwen3  # noqa: F401
+    from ..models import galodra, lekilix, qwen3, senadra  # noqa: F401
 
 
 def read_config_json(model_dir: str) -> Dict[str, Any]:
@@ -104,4 +110,19 @@ def load_model_config(model_dir: str):
     """``(architecture, typed config)`` for a model folder."""
     raw = read_config_json(model_dir)
     arch = architecture_of(raw)
+    if arch.reads_tensor_shapes:
+        raw = arch.with_tensor_sizes(raw, tensor_shapes(model_dir))
     return arch, arch.load_config(raw)
+
+
+def tensor_shapes(model_dir: str) -> Dict[str, tuple]:
+    """Name -> shape of every tensor in the folder's weight file(s); only the headers are read.  Empty without a file."""
+    from ..weights.safetensors_io import SafetensorsError, TensorStore
+    try:
+        store = TensorStore(model_dir)
+    except (FileNotFoundError, SafetensorsError):
+        return {}
+    try:
+        return {name: tuple(store.entry(name).shape) for name in store.names()}
+    finally:
+        store.close()

@@ -1,0 +1,299 @@
+// The gated delta rule with a decay per key channel: a recurrent mixer whose state is a matrix S [dim, vdim] per head.
+//
+// Per token and head, with unit vectors q (times dim^-1/2) and k, a value v, a write strength beta in (0, 1) and a decay
+// g in (0, 1) per key channel:
+//     S <- diag(g) S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q
+// q, k and v come out of a short causal convolution over time (one filter per channel, the last tap is the current
+// token's) followed by silu; the convolution's last `taps - 1` inputs are part of the state.
+//
+// The columns of S are independent: column j is a vector s_j of `dim` numbers with
+//     s_j <- g * s_j;  u_j = beta (v_j - k . s_j);  s_j <- s_j + k u_j;  o_j = q . s_j = q . (g * s_j) + (q . k) u_j
+// so a CTA owns kCols columns of one (sequence, head), kLanes lanes share a column (each holds every kLanes-th entry in
+// registers), and both dot products of a token are taken from the decayed column in ONE pass and reduced together.
+//
+// Kernels:
+//   delta_prep   per token: convolution + silu over the channels q | k | v (inputs of earlier tokens come from the rows
+//                before it in the step, or from the state's tail), unit length of q and k per head, q . k, sigmoid of the
+//                write strength, the decay exp(-exp(A) softplus(z + bias)).  Everything it leaves is float32.
+//   delta_scan   the recurrence over a step's tokens of every sequence, chunks of tokens through shared memory; the CTA
+//                of a sequence's first head and column block also moves the convolution's tail on.
+// State of a slot (float32): S as [heads, vdim, dim] (a column is contiguous), then the tail [taps - 1, channels].
+#include "common.cuh"
+
+namespace iian {
+
+__device__ __forceinline__ float silu_f32(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f32(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+constexpr int kMaxTaps = 8;
+
+// proj rows: [.. q (G * D) | k (G * D) | v (H * V) .. | b (H) ..] at col_off / b_off, row stride ld, activation type A.
+// z: float32 [N, H * D] (the decay's pre-activation without its bias).  taps: float32 [C, n_taps], C = 2 G D + H V.
+template <typename A>
+__global__ void delta_prep_kernel(const A * __restrict__ proj, long long ld, int col_off, int b_off,
+                                  const float * __restrict__ z, const float * __restrict__ taps, int n_taps,
+                                  const float * __restrict__ a_log, const float * __restrict__ dt_bias,
+                                  const float * __restrict__ state, long long state_stride, long long tail_off,
+                                  const int * __restrict__ seq_of_token, const int * __restrict__ cu_q,
+                                  const int * __restrict__ state_slots,
+                                  float * __restrict__ qn, float * __restrict__ kn, float * __restrict__ vv,
+                                  float * __restrict__ beta, float * __restrict__ decay, float * __restrict__ qk,
+                                  int H, int G, int D, int V, float q_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ float act[];            // [2 G D] the activated q | k channels of this token
+    __shared__ float red[32];
+    const size_t t = blockIdx.x;
+    const int s = seq_of_token[t];
+    const int GD = G * D, HV = H * V, C = 2 * GD + HV;
+    if (s < 0) return;                         // padding token: the scan writes zeros for it
+    const int slot = state_slots[s];
+    const int first = cu_q[s];                 // the step's first row of this sequence
+    const float * tail = slot >= 0 ? state + (size_t) slot * state_stride + tail_off : nullptr;
+    const int back = n_taps - 1;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < n_taps; j++) {
+            const long long r = (long long) t - back + j;              // the row that tap j multiplies
+            float x;
+            if (r >= first) x = to_f32(proj[(size_t) r * ld + col_off + c]);
+            else {
+                const int idx = (int) (r - first) + back;              // place in the tail: rows first - back .. first - 1
+                x = (tail != nullptr && idx >= 0) ? tail[(size_t) idx * C + c] : 0.0f;
+            }
+            acc = fmaf(taps[(size_t) c * n_taps + j], x, acc);
+        }
+        const float a = silu_f32(acc);
+        if (c < 2 * GD) act[c] = a;
+        else vv[t * HV + (c - 2 * GD)] = a;
+    }
+    __syncthreads();
+    // unit length per head of q and of k, and q . k: one warp per head
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int g = warp; g < G; g += warps) {
+        const float * qa = act + g * D;
+        const float * ka = act + GD + g * D;
+        float sq = 0.0f, sk = 0.0f, dot = 0.0f;
+        for (int d = lane; d < D; d += 32) {
+            sq = fmaf(qa[d], qa[d], sq);
+            sk = fmaf(ka[d], ka[d], sk);
+            dot = fmaf(qa[d], ka[d], dot);
+        }
+        sq = warp_sum(sq);
+        sk = warp_sum(sk);
+        dot = warp_sum(dot);
+        const float iq = q_scale / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+        for (int d = lane; d < D; d += 32) {
+            qn[t * GD + g * D + d] = qa[d] * iq;
+            kn[t * GD + g * D + d] = ka[d] * ik;
+        }
+        if (lane == 0) qk[t * G + g] = dot * iq * ik;
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        beta[t * H + h] = 1.0f / (1.0f + expf(-to_f32(proj[t * ld + b_off + h])));
+    for (int e = threadIdx.x; e < H * D; e += blockDim.x) {
+        const int h = e / D;
+        decay[t * (size_t) (H * D) + e] = expf(-expf(a_log[h]) * softplus_f32(z[t * (size_t) (H * D) + e] + dt_bias[e]));
+    }
+    (void) red;
+}
+
+constexpr int kCols = 16;        // columns of S a CTA owns
+constexpr int kLanes = 8;        // lanes that share a column
+constexpr int kChunk = 16;       // tokens that wait in shared memory at a time
+
+// E: entries of a column a lane holds (entry d = lane + kLanes * i)
+template <int E, typename A>
+__global__ void __launch_bounds__(kCols * kLanes)
+delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, const float * __restrict__ vv,
+                  const float * __restrict__ beta, const float * __restrict__ decay, const float * __restrict__ qk,
+                  float * __restrict__ state, long long state_stride, long long tail_off,
+                  const A * __restrict__ proj, long long ld, int col_off, int n_taps,
+                  const int * __restrict__ cu_q, const int * __restrict__ state_slots, float * __restrict__ out,
+                  int H, int G, int D, int V) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ float sm[];
+    float * s_q = sm;                          // [kChunk][D]
+    float * s_k = s_q + kChunk * D;            // [kChunk][D]
+    float * s_g = s_k + kChunk * D;            // [kChunk][D]
+    float * s_v = s_g + kChunk * D;            // [kChunk][kCols]
+    float * s_b = s_v + kChunk * kCols;        // [kChunk] beta, [kChunk] q . k
+    const int cb = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
+    const int g = h / (H / G);
+    const int col = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
+    const int j = cb * kCols + col;            // this thread's column of S
+    const int t0 = cu_q[s], t1 = cu_q[s + 1];
+    const int slot = state_slots[s];
+    const int HV = H * V, GD = G * D, HD = H * D;
+    if (slot < 0) {                            // a padding sequence: zeros out, nothing kept
+        for (int t = t0; t < t1; t++)
+            if (lane == 0 && j < V) out[(size_t) t * HV + h * V + j] = 0.0f;
+        return;
+    }
+    float * st = state + (size_t) slot * state_stride;
+    // the convolution's tail moves on: the last taps - 1 inputs of the sequence so far (one CTA per sequence does it)
+    if (cb == 0 && h == 0 && n_taps > 1) {
+        const int C = 2 * GD + HV, back = n_taps - 1, L = t1 - t0;
+        float * tail = st + tail_off;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            float keep[kMaxTaps];
+#pragma unroll
+            for (int i = 0; i < kMaxTaps - 1; i++) {
+                if (i >= back) break;
+                const int src = L - back + i;              // row of the step (relative to t0) that lands at place i
+                keep[i] = src >= 0 ? to_f32(proj[(size_t) (t0 + src) * ld + col_off + c])
+                                   : tail[(size_t) (src + back) * C + c];
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxTaps - 1; i++) {
+                if (i >= back) break;
+                tail[(size_t) i * C + c] = keep[i];
+            }
+        }
+    }
+    float S[E];
+    float * scol = st + ((size_t) h * V + (j < V ? j : 0)) * D;
+#pragma unroll
+    for (int i = 0; i < E; i++) {
+        const int d = lane + kLanes * i;
+        S[i] = (j < V && d < D) ? scol[d] : 0.0f;
+    }
+    for (int c0 = t0; c0 < t1; c0 += kChunk) {
+        const int nt = min(kChunk, t1 - c0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < nt * D; e += blockDim.x) {
+            const int tt = e / D, d = e - tt * D;
+            const size_t t = c0 + tt;
+            s_q[tt * D + d] = qn[t * GD + g * D + d];
+            s_k[tt * D + d] = kn[t * GD + g * D + d];
+            s_g[tt * D + d] = decay[t * HD + h * D + d];
+        }
+        for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
+            const int tt = e / kCols, c = e - tt * kCols;
+            const int jj = cb * kCols + c;
+            s_v[e] = jj < V ? vv[(size_t) (c0 + tt) * HV + h * V + jj] : 0.0f;
+        }
+        for (int e = threadIdx.x; e < nt; e += blockDim.x) {
+            s_b[e] = beta[(size_t) (c0 + e) * H + h];
+            s_b[kChunk + e] = qk[(size_t) (c0 + e) * G + g];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; tt++) {
+            const float * kq = s_k + tt * D;
+            const float * qq = s_q + tt * D;
+            const float * gg = s_g + tt * D;
+            float a = 0.0f, b = 0.0f;
+#pragma unroll
+            for (int i = 0; i < E; i++) {
+                const int d = lane + kLanes * i;
+                if (d < D) {
+                    S[i] *= gg[d];
+                    a = fmaf(kq[d], S[i], a);
+                    b = fmaf(qq[d], S[i], b);
+                }
+            }
+#pragma unroll
+            for (int o = kLanes / 2; o > 0; o >>= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, o);
+                b += __shfl_xor_sync(0xffffffffu, b, o);
+            }
+            const float u = s_b[tt] * (s_v[tt * kCols + col] - a);
+#pragma unroll
+            for (int i = 0; i < E; i++) {
+                const int d = lane + kLanes * i;
+                if (d < D) S[i] = fmaf(kq[d], u, S[i]);
+            }
+            if (lane == 0 && j < V) out[(size_t) (c0 + tt) * HV + h * V + j] = fmaf(s_b[kChunk + tt], u, b);
+        }
+    }
+    if (j < V) {
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            const int d = lane + kLanes * i;
+            if (d < D) scol[d] = S[i];
+        }
+    }
+}
+
+}  // namespace iian
+
+using namespace iian;
+
+// Floats of a slot's state: S [H, V, D], then the tail [taps - 1, 2 G D + H V].
+IIAN_API long long iian_delta_state_floats(int H, int G, int D, int V, int n_taps) {
+    return (long long) H * V * D + (long long) (n_taps - 1) * (2LL * G * D + (long long) H * V);
+}
+
+IIAN_API int iian_delta_prep(const void * proj, long long ld, int col_off, int b_off, int act_dtype, const float * z,
+                             const float * taps, int n_taps, const float * a_log, const float * dt_bias, const float * state,
+                             long long state_stride, const int * seq_of_token, const int * cu_q, const int * state_slots,
+                             float * qn, float * kn, float * vv, float * beta, float * decay, float * qk, int N, int H, int G,
+                             int D, int V, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0 || n_taps < 1 || n_taps > kMaxTaps) return IIAN_ERR_SHAPE;
+    const size_t smem = (size_t) 2 * G * D * sizeof(float);
+    if (smem > 200 * 1024) return IIAN_ERR_LIMIT;
+    const long long tail_off = (long long) H * V * D;
+    const float q_scale = 1.0f / sqrtf((float) D);
+    if (act_dtype == IIAN_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        return iian_launch(delta_prep_kernel<float>, dim3(N), dim3(256), smem, stream, (const float *) proj, ld, col_off, b_off, z,
+                           taps, n_taps, a_log, dt_bias, state, state_stride, tail_off, seq_of_token, cu_q, state_slots, qn, kn,
+                           vv, beta, decay, qk, H, G, D, V, q_scale);
+    }
+    if (act_dtype == IIAN_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        return iian_launch(delta_prep_kernel<__nv_bfloat16>, dim3(N), dim3(256), smem, stream, (const __nv_bfloat16 *) proj, ld,
+                           col_off, b_off, z, taps, n_taps, a_log, dt_bias, state, state_stride, tail_off, seq_of_token, cu_q,
+                           state_slots, qn, kn, vv, beta, decay, qk, H, G, D, V, q_scale);
+    }
+    return IIAN_ERR_DTYPE;
+}
+
+template <int E, typename A>
+static int launch_scan(const float * qn, const float * kn, const float * vv, const float * beta, const float * decay,
+                       const float * qk, float * state, long long state_stride, const A * proj, long long ld, int col_off,
+                       int n_taps, const int * cu_q, const int * state_slots, float * out, int S, int H, int G, int D, int V,
+                       cudaStream_t stream) {
+    const size_t smem = ((size_t) kChunk * (3 * D + kCols) + 2 * kChunk) * sizeof(float);
+    if (smem > 200 * 1024) return IIAN_ERR_LIMIT;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<E, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+    const dim3 grid((V + kCols - 1) / kCols, H, S);
+    return iian_launch(delta_scan_kernel<E, A>, grid, dim3(kCols * kLanes), smem, stream, qn, kn, vv, beta, decay, qk, state,
+                       state_stride, (long long) H * V * D, proj, ld, col_off, n_taps, cu_q, state_slots, out, H, G, D, V);
+}
+
+template <typename A>
+static int scan_by_depth(const float * qn, const float * kn, const float * vv, const float * beta, const float * decay,
+                         const float * qk, float * state, long long state_stride, const A * proj, long long ld, int col_off,
+                         int n_taps, const int * cu_q, const int * state_slots, float * out, int S, int H, int G, int D, int V,
+                         cudaStream_t stream) {
+    const int e = (D + kLanes - 1) / kLanes;
+#define IIAN_SCAN(E) return launch_scan<E, A>(qn, kn, vv, beta, decay, qk, state, state_stride, proj, ld, col_off, n_taps, cu_q, \
+                                              state_slots, out, S, H, G, D, V, stream)
+    if (e <= 2) IIAN_SCAN(2);
+    if (e <= 4) IIAN_SCAN(4);
+    if (e <= 8) IIAN_SCAN(8);
+    if (e <= 16) IIAN_SCAN(16);
+    if (e <= 32) IIAN_SCAN(32);
+    if (e <= 64) IIAN_SCAN(64);
+#undef IIAN_SCAN
+    return IIAN_ERR_LIMIT;
+}
+
+// out: float32 [N, H * V].  S sequences (grid z); a sequence with state slot -1 is padding.
+IIAN_API int iian_delta_scan(const float * qn, const float * kn, const float * vv, const float * beta, const float * decay,
+                             const float * qk, float * state, long long state_stride, const void * proj, long long ld,
+                             int col_off, int act_dtype, int n_taps, const int * cu_q, const int * state_slots, float * out,
+                             int S, int H, int G, int D, int V, cudaStream_t stream) {
+    if (S <= 0) return IIAN_OK;
+    if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0 || n_taps < 1 || n_taps > kMaxTaps || S > 65535 || H > 65535) return IIAN_ERR_SHAPE;
+    if (act_dtype == IIAN_F32)
+        return scan_by_depth<float>(qn, kn, vv, beta, decay, qk, state, state_stride, (const float *) proj, ld, col_off, n_taps,
+                                    cu_q, state_slots, out, S, H, G, D, V, stream);
+    if (act_dtype == IIAN_BF16)
+        return scan_by_depth<__nv_bfloat16>(qn, kn, vv, beta, decay, qk, state, state_stride, (const __nv_bfloat16 *) proj, ld,
+                                            col_off, n_taps, cu_q, state_slots, out, S, H, G, D, V, stream);
+    return IIAN_ERR_DTYPE;
+}

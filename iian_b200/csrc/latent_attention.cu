@@ -25,10 +25,26 @@ constexpr int kLatWarps = 4;
 constexpr int kLatMaxRank = 1024;
 constexpr int kLatMaxWidth = 1536;       // rank + rot
 
-// qd row: [.. q (H * (dim + rot)) .. dkv (rank + rot) ..] at q_off / dkv_off, row stride ld.
+// Entry i of a vector after the rotation of its first rot_dims entries.  style 0 pairs entry i with entry i + rot_dims / 2,
+// style 1 pairs entry 2 i with entry 2 i + 1; pair number n turns by the angle whose cos and sin are cs_sn[2 n], [2 n + 1].
+template <typename A>
+__device__ __forceinline__ float rotated_entry(const A * v, int i, int half, int rot_dims, int style, const float * cs_sn) {
+    if (i >= rot_dims) return to_f32(v[i]);
+    if (style == 1) {
+        const int n = i >> 1;
+        return (i & 1) ? rot_hi(to_f32(v[i - 1]), to_f32(v[i]), cs_sn[2 * n], cs_sn[2 * n + 1])
+                       : rot_lo(to_f32(v[i]), to_f32(v[i + 1]), cs_sn[2 * n], cs_sn[2 * n + 1]);
+    }
+    if (i < half) return rot_lo(to_f32(v[i]), to_f32(v[i + half]), cs_sn[2 * i], cs_sn[2 * i + 1]);
+    return rot_hi(to_f32(v[i - half]), to_f32(v[i]), cs_sn[2 * (i - half)], cs_sn[2 * (i - half) + 1]);
+}
+
+// qd row: [.. q (H * (dim + rot)) .. dkv (rank + rot) ..] at q_off / dkv_off, row stride ld; with `qm` the queries are
+// rows of a matrix of their own (row stride ld_q) instead.
 // cache rows: [cells, rank + rot].  q_cat rows: [H, rank + rot]; this kernel fills [rank, rank + rot) of every head.
 template <typename A>
 __global__ void latent_prep_kernel(const A * __restrict__ qd, long long ld, int q_off, int dkv_off,
+                                   const A * __restrict__ qm, long long ld_q, int style,
                                    A * __restrict__ cache, A * __restrict__ q_cat, const float * __restrict__ norm_w,
                                    const double * __restrict__ inv_freq, const int * __restrict__ positions,
                                    const int * __restrict__ slots, int H, int dim, int rot, int rank, int rot_dims,
@@ -63,24 +79,14 @@ __global__ void latent_prep_kernel(const A * __restrict__ qd, long long ld, int 
         A * crow = cache + (size_t) cell * width;
         for (int i = threadIdx.x; i < rank; i += blockDim.x) crow[i] = from_f32<A>(to_f32(dkv[i]) * inv * norm_w[i]);
         const A * kr = dkv + rank;
-        for (int i = threadIdx.x; i < rot; i += blockDim.x) {
-            float y;
-            if (i < half) y = rot_lo(to_f32(kr[i]), to_f32(kr[i + half]), cs_sn[2 * i], cs_sn[2 * i + 1]);
-            else if (i < rot_dims) y = rot_hi(to_f32(kr[i - half]), to_f32(kr[i]), cs_sn[2 * (i - half)], cs_sn[2 * (i - half) + 1]);
-            else y = to_f32(kr[i]);
-            crow[rank + i] = from_f32<A>(y);
-        }
+        for (int i = threadIdx.x; i < rot; i += blockDim.x) crow[rank + i] = from_f32<A>(rotated_entry(kr, i, half, rot_dims, style, cs_sn));
     }
     // the rotated part of every query head
-    const A * q = row + q_off;
+    const A * q = qm != nullptr ? qm + t * ld_q : row + q_off;
     for (int e = threadIdx.x; e < H * rot; e += blockDim.x) {
         const int h = e / rot, i = e - h * rot;
         const A * qr = q + (size_t) h * (dim + rot) + dim;
-        float y;
-        if (i < half) y = rot_lo(to_f32(qr[i]), to_f32(qr[i + half]), cs_sn[2 * i], cs_sn[2 * i + 1]);
-        else if (i < rot_dims) y = rot_hi(to_f32(qr[i - half]), to_f32(qr[i]), cs_sn[2 * (i - half)], cs_sn[2 * (i - half) + 1]);
-        else y = to_f32(qr[i]);
-        q_cat[(t * H + h) * width + rank + i] = from_f32<A>(y);
+        q_cat[(t * H + h) * width + rank + i] = from_f32<A>(rotated_entry(qr, i, half, rot_dims, style, cs_sn));
     }
 }
 
@@ -283,23 +289,34 @@ __global__ void latent_attention_kernel(const A * __restrict__ q, const A * __re
 
 using namespace iian;
 
-IIAN_API int iian_latent_prep(const void * qd, long long ld, int q_off, int dkv_off, void * cache, void * q_cat,
-                              const float * norm_w, const double * inv_freq, const int * positions, const int * slots,
-                              int act_dtype, int N, int H, int dim, int rot, int rank, int rot_dims, float eps,
-                              long long n_cells, cudaStream_t stream) {
+// qm: the queries as rows of a matrix of their own (row stride ld_q), or null: then they sit in qd at q_off.
+// style: 0 pairs entry i with entry i + rot_dims / 2, 1 pairs entry 2 i with entry 2 i + 1.
+IIAN_API int iian_latent_prep_split(const void * qd, long long ld, int q_off, int dkv_off, const void * qm, long long ld_q,
+                                    int style, void * cache, void * q_cat, const float * norm_w, const double * inv_freq,
+                                    const int * positions, const int * slots, int act_dtype, int N, int H, int dim, int rot,
+                                    int rank, int rot_dims, float eps, long long n_cells, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
-    if (rot_dims < 0 || rot_dims % 2 || rot_dims > rot || rank <= 0 || H <= 0 || dim < 0) return IIAN_ERR_SHAPE;
+    if (rot_dims < 0 || rot_dims % 2 || rot_dims > rot || rank <= 0 || H <= 0 || dim < 0 || (style != 0 && style != 1)) return IIAN_ERR_SHAPE;
     const size_t smem = (size_t) (rot_dims > 0 ? rot_dims : 2) * sizeof(float);
     if (smem > 40 * 1024) return IIAN_ERR_LIMIT;
     const int threads = 128;
     if (act_dtype == IIAN_F32)
         return iian_launch(latent_prep_kernel<float>, dim3(N), dim3(threads), smem, stream, (const float *) qd, ld, q_off, dkv_off,
-                           (float *) cache, (float *) q_cat, norm_w, inv_freq, positions, slots, H, dim, rot, rank, rot_dims, eps, n_cells);
+                           (const float *) qm, ld_q, style, (float *) cache, (float *) q_cat, norm_w, inv_freq, positions, slots, H,
+                           dim, rot, rank, rot_dims, eps, n_cells);
     if (act_dtype == IIAN_BF16)
         return iian_launch(latent_prep_kernel<__nv_bfloat16>, dim3(N), dim3(threads), smem, stream, (const __nv_bfloat16 *) qd, ld,
-                           q_off, dkv_off, (__nv_bfloat16 *) cache, (__nv_bfloat16 *) q_cat, norm_w, inv_freq, positions, slots, H,
-                           dim, rot, rank, rot_dims, eps, n_cells);
+                           q_off, dkv_off, (const __nv_bfloat16 *) qm, ld_q, style, (__nv_bfloat16 *) cache,
+                           (__nv_bfloat16 *) q_cat, norm_w, inv_freq, positions, slots, H, dim, rot, rank, rot_dims, eps, n_cells);
     return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_latent_prep(const void * qd, long long ld, int q_off, int dkv_off, void * cache, void * q_cat,
+                              const float * norm_w, const double * inv_freq, const int * positions, const int * slots,
+                              int act_dtype, int N, int H, int dim, int rot, int rank, int rot_dims, float eps,
+                              long long n_cells, cudaStream_t stream) {
+    return iian_latent_prep_split(qd, ld, q_off, dkv_off, nullptr, 0, 0, cache, q_cat, norm_w, inv_freq, positions, slots,
+                                  act_dtype, N, H, dim, rot, rank, rot_dims, eps, n_cells, stream);
 }
 
 IIAN_API int iian_head_linear(const void * in, long long ld_in, int in_hs, const void * w, int w_dtype, long long w_hs,

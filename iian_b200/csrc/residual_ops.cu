@@ -1,0 +1,203 @@
+// Row-wise kernels around a residual stream whose sub-layer outputs are added with a factor, a feed-forward activation with
+// two learned numbers, a second token-indexed input per layer, and a cap on the logits.
+//
+//   scaled_add_rms_norm   x += m * d (float32, in place);  out = x / sqrt(mean(x^2) + eps) * w      (d, out optional)
+//   scaled_add_unit_rms   x += m * y / sqrt(mean(y^2) + eps) * w                                     a normalised addend
+//   gelu_mul_table        out[r, :] = gelu_tanh(g[r, :]) * table[token(r), off : off + n]            token(r) = tokens[rows ? rows[r] : r]
+//   rms_norm_rows         out = x / sqrt(mean(x^2) + eps) * w for rows x of a wider matrix (row stride ld)
+//   xielu                 z > 0: softplus(p) z^2 + z / 2;  else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+//   tanh_cap              z <- cap * tanh(z / cap), in place
+//
+// `A` is the activation type; sums, norms and the stream are float32.  A row's result depends on that row only.
+#include "common.cuh"
+
+namespace iian {
+
+template <typename A>
+__global__ void scaled_add_rms_norm_kernel(float * __restrict__ residual, const A * __restrict__ delta, float mult,
+                                           const float * __restrict__ weight, A * __restrict__ out, A * __restrict__ copy,
+                                           int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    float * r = residual + base;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (delta != nullptr) {
+            v = fmaf(mult, to_f32(delta[base + i]), v);
+            r[i] = v;
+        }
+        if (copy != nullptr) copy[base + i] = from_f32<A>(v);
+        ss = fmaf(v, v, ss);
+    }
+    if (out == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float) H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[base + i] = from_f32<A>(r[i] * inv * weight[i]);
+}
+
+template <typename A>
+__global__ void scaled_add_unit_rms_kernel(float * __restrict__ residual, const A * __restrict__ y, float mult,
+                                           const float * __restrict__ weight, int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_f32(y[base + i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = mult / sqrtf(ss / (float) H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        residual[base + i] = fmaf(to_f32(y[base + i]) * inv, weight[i], residual[base + i]);
+}
+
+template <typename A>
+__global__ void rms_norm_rows_kernel(const A * __restrict__ x, long long ld, const float * __restrict__ weight,
+                                     A * __restrict__ out, int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const A * r = x + (size_t) blockIdx.x * ld;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_f32(r[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float) H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[(size_t) blockIdx.x * H + i] = from_f32<A>(to_f32(r[i]) * inv * weight[i]);
+}
+
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename A, typename W>
+__global__ void gelu_mul_table_kernel(const A * __restrict__ g, const W * __restrict__ table, long long ld_table, int off,
+                                      const int * __restrict__ tokens, const int * __restrict__ rows, A * __restrict__ out,
+                                      long long total, int n, int vocab) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long e = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const long long r = e / n;
+    const int c = (int) (e - r * n);
+    int tok = tokens[rows != nullptr ? rows[r] : r];
+    tok = min(max(tok, 0), vocab - 1);
+    out[e] = from_f32<A>(gelu_tanh_f32(to_f32(g[e])) * to_f32(table[(size_t) tok * ld_table + off + c]));
+}
+
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+template <typename A>
+__global__ void xielu_kernel(const A * __restrict__ x, const float * __restrict__ pq, A * __restrict__ out, long long total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long e = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= total) return;
+    const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
+    const float z = to_f32(x[e]);
+    const float y = z > 0.0f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+    out[e] = from_f32<A>(y);
+}
+
+__global__ void tanh_cap_kernel(float * __restrict__ x, float cap, long long total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long e = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < total) x[e] = cap * tanhf(x[e] / cap);
+}
+
+}  // namespace iian
+
+using namespace iian;
+
+// delta, out, copy may be null: without delta nothing is added; without out no norm is taken; copy receives the new
+// stream in the activation type.
+IIAN_API int iian_scaled_add_rms_norm(float * residual, const void * delta, float mult, const float * weight, void * out,
+                                      void * copy, int act_dtype, int N, int H, float eps, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (H <= 0) return IIAN_ERR_SHAPE;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (act_dtype == IIAN_F32)
+        return iian_launch(scaled_add_rms_norm_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float *) delta,
+                           mult, weight, (float *) out, (float *) copy, H, eps);
+    if (act_dtype == IIAN_BF16)
+        return iian_launch(scaled_add_rms_norm_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, residual,
+                           (const __nv_bfloat16 *) delta, mult, weight, (__nv_bfloat16 *) out, (__nv_bfloat16 *) copy, H, eps);
+    return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_scaled_add_unit_rms(float * residual, const void * y, float mult, const float * weight, int act_dtype, int N,
+                                      int H, float eps, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (H <= 0) return IIAN_ERR_SHAPE;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (act_dtype == IIAN_F32)
+        return iian_launch(scaled_add_unit_rms_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float *) y, mult,
+                           weight, H, eps);
+    if (act_dtype == IIAN_BF16)
+        return iian_launch(scaled_add_unit_rms_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, residual,
+                           (const __nv_bfloat16 *) y, mult, weight, H, eps);
+    return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_rms_norm_rows(const void * x, long long ld, const float * weight, void * out, int act_dtype, int N, int H,
+                                float eps, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (H <= 0) return IIAN_ERR_SHAPE;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (act_dtype == IIAN_F32)
+        return iian_launch(rms_norm_rows_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) x, ld, weight, (float *) out, H, eps);
+    if (act_dtype == IIAN_BF16)
+        return iian_launch(rms_norm_rows_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) x, ld, weight,
+                           (__nv_bfloat16 *) out, H, eps);
+    return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_gelu_mul_table(const void * g, const void * table, int table_dtype, long long ld_table, int off,
+                                 const int * tokens, const int * rows, void * out, int act_dtype, int R, int n, int vocab,
+                                 cudaStream_t stream) {
+    const long long total = (long long) R * n;
+    if (total <= 0) return IIAN_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
+    if (act_dtype == IIAN_F32 && table_dtype == IIAN_F32)
+        return iian_launch(gelu_mul_table_kernel<float, float>, dim3(blocks), dim3(threads), 0, stream, (const float *) g,
+                           (const float *) table, ld_table, off, tokens, rows, (float *) out, total, n, vocab);
+    if (act_dtype == IIAN_BF16 && table_dtype == IIAN_BF16)
+        return iian_launch(gelu_mul_table_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream,
+                           (const __nv_bfloat16 *) g, (const __nv_bfloat16 *) table, ld_table, off, tokens, rows,
+                           (__nv_bfloat16 *) out, total, n, vocab);
+    if (act_dtype == IIAN_BF16 && table_dtype == IIAN_F32)
+        return iian_launch(gelu_mul_table_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(threads), 0, stream,
+                           (const __nv_bfloat16 *) g, (const float *) table, ld_table, off, tokens, rows, (__nv_bfloat16 *) out,
+                           total, n, vocab);
+    return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_xielu(const void * x, const float * pq, void * out, int act_dtype, long long total, cudaStream_t stream) {
+    if (total <= 0) return IIAN_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
+    if (act_dtype == IIAN_F32)
+        return iian_launch(xielu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) x, pq, (float *) out, total);
+    if (act_dtype == IIAN_BF16)
+        return iian_launch(xielu_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16 *) x, pq,
+                           (__nv_bfloat16 *) out, total);
+    return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_tanh_cap(float * x, float cap, long long total, cudaStream_t stream) {
+    if (total <= 0) return IIAN_OK;
+    if (!(cap > 0.0f)) return IIAN_ERR_SHAPE;
+    const int threads = 256;
+    const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
+    return iian_launch(tanh_cap_kernel, dim3(blocks), dim3(threads), 0, stream, x, cap, total);
+}

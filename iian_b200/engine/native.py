@@ -134,7 +134,8 @@ def supports(model) -> bool:
     from ..parts.norm import RMSNorm
     from ..parts.position import NoPosition, Rotary
     if model.device.type != "cuda" or type(model.embedding) is not TokenEmbedding or type(model.head) is not LMHead \
-            or type(model.final_norm) is not RMSNorm or model.embedding.scale != 1.0 or model.stream_parts:
+            or type(model.final_norm) is not RMSNorm or model.embedding.scale != 1.0 or model.stream_parts \
+            or model.embedding.side_width or model.head.softcap is not None:
         return False
     for blk in model.blocks:
         if type(blk) is not PreNormResidualBlock or type(blk.mixer) is not Attention or type(blk.feed_forward) is not GatedMLP \

@@ -926,11 +926,12 @@ class CudaKernels:
     def latent_prep(self, qd: torch.Tensor, q_off: int, dkv_off: int, cache_rows: Optional[torch.Tensor], q_cat: torch.Tensor,
                     norm_weight: torch.Tensor, inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
                     slots: Optional[torch.Tensor], *, num_heads: int, dim: int, rot: int, rank: int, rot_dims: int,
-                    eps: float) -> None:
+                    eps: float, queries: Optional[torch.Tensor] = None, style: int = 0) -> None:
         """From the projected rows ``qd`` (queries at column ``q_off``, the down-projected latent and shared key part at
         ``dkv_off``): normalise the latent, rotate the key part, store both at the token's cache cell, and put the
         rotated part of every query head behind the ``rank`` columns of its row of ``q_cat`` [N, H, rank + rot].
-        ``inv_freq`` is float64 [rot_dims / 2]."""
+        ``inv_freq`` is float64 [rot_dims / 2].  ``queries``: the queries as a matrix of their own [N, heads * (dim + rot)]
+        (then ``q_off`` is not used); ``style`` 0 rotates entry i with entry i + rot_dims / 2, 1 entry 2i with entry 2i + 1."""
         n = qd.shape[0]
         width = rank + rot
         if q_cat.shape != (n, num_heads, width) or q_cat.dtype != qd.dtype:
@@ -941,10 +942,13 @@ class CudaKernels:
                 raise KernelError(f"latent_prep: cache {tuple(cache_rows.shape)} {cache_rows.dtype} does not match")
             n_cells = cache_rows.numel() // width
         qp, ld = self._rows(qd, "projected rows")
-        fn = _fn("latent_attention", "iian_latent_prep",
-                 [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p])
-        _check(fn(qp, ld, q_off, dkv_off, _cuda(cache_rows, "latent cache"), _cuda(q_cat, "q_cat"),
+        qm, ld_q = self._rows(queries, "queries")
+        if queries is not None and (queries.shape != (n, num_heads * (dim + rot)) or queries.dtype != qd.dtype):
+            raise KernelError("latent_prep: queries must be [N, heads * (dim + rot)] in the activation dtype")
+        fn = _fn("latent_attention", "iian_latent_prep_split",
+                 [c_void_p, c_longlong, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong, c_void_p])
+        _check(fn(qp, ld, q_off, dkv_off, qm, ld_q, style, _cuda(cache_rows, "latent cache"), _cuda(q_cat, "q_cat"),
                   _cuda(norm_weight, "latent norm weight", torch.float32), _cuda(inv_freq, "inv_freq", torch.float64),
                   _cuda(positions, "positions", torch.int32), _cuda(slots if cache_rows is not None else None, "slots", torch.int32),
                   _code(qd, "projected rows"), n, num_heads, dim, rot, rank, rot_dims if inv_freq is not None else 0, eps,
@@ -1345,6 +1349,160 @@ class CudaKernels:
         """Floats of one column block of the state: the block's columns, a copy of the normaliser, the running maximum,
         padded to a multiple of 4 (csrc/matrix_memory.cu: iian_matrix_memory_block_floats)."""
         return ((columns + 1) * dim + 1 + 3) // 4 * 4
+
+    # ---- scaled residual sums, a normalised addend, xIELU, a token-indexed factor, the logit cap (csrc/residual_ops.cu) ----
+    def scaled_add_rms_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], mult: float, weight: Optional[torch.Tensor],
+                            eps: float, out: Optional[torch.Tensor], copy: Optional[torch.Tensor] = None) -> None:
+        """``residual += mult * delta`` (float32, in place; nothing without ``delta``); ``out`` (optional) receives
+        ``residual / sqrt(mean(residual^2) + eps) * weight``; ``copy`` (optional) the new stream in the activation dtype."""
+        n, h = residual.shape
+        act = out if out is not None else copy if copy is not None else delta
+        if act is None:
+            return
+        for name, t in (("delta", delta), ("out", out), ("copy", copy)):
+            if t is not None and (t.shape != residual.shape or t.dtype != act.dtype):
+                raise KernelError(f"scaled_add_rms_norm: {name} {tuple(t.shape)} {t.dtype} does not match the stream {tuple(residual.shape)}")
+        if out is not None and (weight is None or weight.numel() != h):
+            raise KernelError("scaled_add_rms_norm: the norm's weight does not match the stream")
+        fn = _fn("residual_ops", "iian_scaled_add_rms_norm",
+                 [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(_cuda(residual, "residual", torch.float32), _cuda(delta, "delta"), mult, _cuda(weight, "norm weight", torch.float32),
+                  _cuda(out, "norm out"), _cuda(copy, "stream copy"), _code(act, "norm out"), n, h, eps, _stream()), "scaled_add_rms_norm")
+
+    def scaled_add_unit_rms(self, residual: torch.Tensor, y: torch.Tensor, mult: float, weight: torch.Tensor, eps: float) -> None:
+        """``residual += mult * y / sqrt(mean(y^2) + eps) * weight`` (float32, in place)."""
+        n, h = residual.shape
+        if y.shape != (n, h) or weight.numel() != h:
+            raise KernelError("scaled_add_unit_rms: shapes do not fit")
+        fn = _fn("residual_ops", "iian_scaled_add_unit_rms", [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(_cuda(residual, "residual", torch.float32), _cuda(y, "addend"), mult, _cuda(weight, "norm weight", torch.float32),
+                  _code(y, "addend"), n, h, eps, _stream()), "scaled_add_unit_rms")
+
+    def rms_norm_rows(self, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+        """``out = x / sqrt(mean(x^2) + eps) * weight`` where ``x`` may be a column slice of a wider matrix."""
+        n, h = x.shape
+        xp, ld = self._rows(x, "rms_norm_rows in")
+        if out.shape != (n, h) or out.dtype != x.dtype or weight.numel() != h:
+            raise KernelError("rms_norm_rows: out / weight do not match the input")
+        fn = _fn("residual_ops", "iian_rms_norm_rows", [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(xp, ld, _cuda(weight, "norm weight", torch.float32), _cuda(out, "rms_norm_rows out"), _code(x, "rms_norm_rows in"),
+                  n, h, eps, _stream()), "rms_norm_rows")
+
+    def gelu_mul_table(self, g: torch.Tensor, table: torch.Tensor, col_off: int, tokens: torch.Tensor, rows: Optional[torch.Tensor],
+                       out: torch.Tensor) -> None:
+        """``out[r] = gelu_tanh(g[r]) * table[token(r), col_off : col_off + n]``, ``token(r) = tokens[rows[r]]`` (``tokens[r]``
+        without ``rows``)."""
+        r, n = g.shape
+        if out.shape != (r, n) or out.dtype != g.dtype or table.dim() != 2 or col_off < 0 or col_off + n > table.shape[1] \
+                or (rows is not None and rows.numel() != r) or (rows is None and tokens.numel() < r):
+            raise KernelError("gelu_mul_table: shapes do not fit")
+        fn = _fn("residual_ops", "iian_gelu_mul_table",
+                 [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(g, "gate"), _cuda(table, "table"), _code(table, "table"), table.shape[1], col_off, _cuda(tokens, "tokens", torch.int32),
+                  _cuda(rows, "rows", torch.int32), _cuda(out, "gated out"), _code(g, "gate"), r, n, table.shape[0], _stream()),
+               "gelu_mul_table")
+
+    def xielu(self, x: torch.Tensor, pq: torch.Tensor, out: torch.Tensor) -> None:
+        """``z > 0: softplus(p) z^2 + z / 2; else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2`` with ``pq`` = float32 [p, q]."""
+        if out.shape != x.shape or out.dtype != x.dtype or pq.numel() != 2:
+            raise KernelError("xielu: shapes or dtypes do not fit")
+        fn = _fn("residual_ops", "iian_xielu", [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+        _check(fn(_cuda(x, "xielu in"), _cuda(pq, "xielu numbers", torch.float32), _cuda(out, "xielu out"), _code(x, "xielu in"),
+                  x.numel(), _stream()), "xielu")
+
+    def tanh_cap(self, x: torch.Tensor, cap: float) -> None:
+        """``x <- cap * tanh(x / cap)`` in place (float32)."""
+        fn = _fn("residual_ops", "iian_tanh_cap", [c_void_p, c_float, c_longlong, c_void_p])
+        _check(fn(_cuda(x, "capped values", torch.float32), cap, x.numel(), _stream()), "tanh_cap")
+
+    # ---- attention inside chunks of positions with a penalty on distance (csrc/chunked_attention.cu) -----------------------
+    def kv_store_normed(self, proj: torch.Tensor, k_off: int, v_off: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                        slots: torch.Tensor, *, num_kv_heads: int, k_dim: int, v_dim: int, eps: float, norm_values: bool) -> None:
+        """Per token: the keys at column ``k_off`` of ``proj`` as they are, the values at ``v_off`` divided by their root mean
+        square per head (if ``norm_values``), into the token's cells of ``k_cache`` [pages, kv_heads, page_size, k_dim] and
+        ``v_cache`` [.., v_dim]."""
+        n = proj.shape[0]
+        pp, ld = self._rows(proj, "projections")
+        if k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != k_dim or v_cache.shape[3] != v_dim or k_cache.shape[:3] != v_cache.shape[:3] \
+                or k_cache.dtype != proj.dtype or v_cache.dtype != proj.dtype or slots.numel() != n:
+            raise KernelError(f"kv_store_normed: caches {tuple(k_cache.shape)} / {tuple(v_cache.shape)} do not fit")
+        fn = _fn("chunked_attention", "iian_kv_store_normed",
+                 [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,
+                  c_float, c_int, c_void_p])
+        _check(fn(pp, ld, k_off, v_off, _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"), _cuda(slots, "slots", torch.int32),
+                  _code(proj, "projections"), n, num_kv_heads, k_dim, v_dim, k_cache.shape[2], k_cache.shape[0] * k_cache.shape[2], eps,
+                  1 if norm_values else 0, _stream()), "kv_store_normed")
+
+    def chunked_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, meta, *,
+                          num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float, chunk: Optional[int],
+                          window: Optional[int], r1: Optional[torch.Tensor], r2: Optional[torch.Tensor],
+                          gate: Optional[torch.Tensor]) -> None:
+        """``q`` rows of ``heads * k_dim`` (may be a column slice) -> ``out`` [N, heads * v_dim]: softmax of
+        ``q . k * scale - r1 ln(1 + r2 (i - j))`` over the keys ``j <= i`` of position ``i``'s chunk (or window), weighted sum
+        of the cached values, times ``sigmoid(gate)`` if given (rows of ``heads * v_dim``, may be a column slice)."""
+        n = q.shape[0]
+        qp, ld_q = self._rows(q, "queries")
+        gp, ld_g = self._rows(gate, "gate")
+        if q.shape[1] != num_heads * k_dim or out.shape != (n, num_heads * v_dim) or out.dtype != q.dtype or k_cache.dtype != q.dtype \
+                or (gate is not None and (gate.shape != out.shape or gate.dtype != q.dtype)) or (r1 is None) != (r2 is None):
+            raise KernelError(f"chunked_attention: q {tuple(q.shape)}, out {tuple(out.shape)} do not fit")
+        bt = meta.block_table
+        fn = _fn("chunked_attention", "iian_chunked_attention",
+                 [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p])
+        _check(fn(qp, ld_q, _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"), _cuda(out, "attention out"),
+                  _cuda(meta.positions, "positions", torch.int32), _cuda(meta.seq_of_token, "seq_of_token", torch.int32),
+                  _cuda(bt, "block table", torch.int32), bt.shape[1], _cuda(meta.ctx_len, "ctx_len", torch.int32), _code(q, "queries"),
+                  n, num_heads, num_kv_heads, k_dim, v_dim, k_cache.shape[2], k_cache.shape[0], scale, chunk or 0, window or 0,
+                  _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g, _stream()), "chunked_attention")
+
+    # ---- the delta rule with a decay per key channel (csrc/delta_rule.cu) ---------------------------------------------------
+    @staticmethod
+    def delta_state_floats(num_heads: int, num_kv_heads: int, dim: int, v_dim: int, taps: int) -> int:
+        """Floats of a request's state: S [heads, v_dim, dim], then the convolution's tail [taps - 1, channels]
+        (csrc/delta_rule.cu: iian_delta_state_floats)."""
+        return num_heads * v_dim * dim + (taps - 1) * (2 * num_kv_heads * dim + num_heads * v_dim)
+
+    def delta_rule(self, proj: torch.Tensor, col_off: int, b_off: int, z: torch.Tensor, taps: torch.Tensor, a_log: torch.Tensor,
+                   dt_bias: torch.Tensor, state: torch.Tensor, ctx, out: torch.Tensor, *, num_heads: int, num_kv_heads: int, dim: int,
+                   v_dim: int) -> None:
+        """The recurrence over this step's tokens of every sequence.  ``proj`` rows hold the convolution's inputs q | k | v at
+        column ``col_off`` and the write strengths' pre-activations at ``b_off``; ``z`` float32 [N, heads * dim] the decays'
+        pre-activations without bias; ``taps`` float32 [channels, taps]; ``state`` float32 [slots, state floats];
+        ``out`` float32 [N, heads * v_dim] receives ``S^T q`` per head.  Two launches: per-token preparation, then the scan."""
+        n = proj.shape[0]
+        h, g, d, v = num_heads, num_kv_heads, dim, v_dim
+        channels = 2 * g * d + h * v
+        n_taps = taps.shape[1]
+        pp, ld = self._rows(proj, "projections")
+        s = ctx.cu_q.numel() - 1
+        if z.shape != (n, h * d) or taps.shape[0] != channels or a_log.numel() != h or dt_bias.numel() != h * d \
+                or out.shape != (n, h * v) or state.dim() != 2 or state.shape[1] != self.delta_state_floats(h, g, d, v, n_taps) \
+                or ctx.state_slots.numel() != s:
+            raise KernelError("delta_rule: shapes do not fit")
+        f32 = torch.float32
+        qn = ctx.buf("delta_q", (n, g * d), f32)
+        kn = ctx.buf("delta_k", (n, g * d), f32)
+        vv = ctx.buf("delta_v", (n, h * v), f32)
+        beta = ctx.buf("delta_beta", (n, h), f32)
+        decay = ctx.buf("delta_decay", (n, h * d), f32)
+        qk = ctx.buf("delta_qk", (n, g), f32)
+        code = _code(proj, "projections")
+        fn = _fn("delta_rule", "iian_delta_prep",
+                 [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
+                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                  c_int, c_void_p])
+        _check(fn(pp, ld, col_off, b_off, code, _cuda(z, "decay pre-activations", f32), _cuda(taps, "taps", f32), n_taps,
+                  _cuda(a_log, "A_log", f32), _cuda(dt_bias, "dt_bias", f32), _cuda(state, "state", f32), state.shape[1],
+                  _cuda(ctx.seq_of_token, "seq_of_token", torch.int32), _cuda(ctx.cu_q, "cu_q", torch.int32),
+                  _cuda(ctx.state_slots, "state slots", torch.int32), qn.data_ptr(), kn.data_ptr(), vv.data_ptr(), beta.data_ptr(),
+                  decay.data_ptr(), qk.data_ptr(), n, h, g, d, v, _stream()), "delta_prep")
+        fn = _fn("delta_rule", "iian_delta_scan",
+                 [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int,
+                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(qn.data_ptr(), kn.data_ptr(), vv.data_ptr(), beta.data_ptr(), decay.data_ptr(), qk.data_ptr(), state.data_ptr(),
+                  state.shape[1], pp, ld, col_off, code, n_taps, ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(),
+                  _cuda(out, "delta out", f32), s, h, g, d, v, _stream()), "delta_scan")
 
     # ---- routing by a table, weights on the experts' outputs (csrc/moe.cu) ------------------------------------------------------
     def moe_table_route(self, tokens: torch.Tensor, rows: Optional[torch.Tensor], table: torch.Tensor, num_experts: int,

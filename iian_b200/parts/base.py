@@ -55,11 +55,17 @@ from ..weights.loader import TensorSpec
 @dataclass(frozen=True)
 class KVNeed:
     """Per-token entries: keys and values of ``num_kv_heads`` heads of ``head_dim``; ``window`` = how
-    many of the latest keys stay needed (None: all)."""
+    many of the latest keys stay needed (None: all); ``v_dim``: the size of a value where it differs from a key's
+    (None: ``head_dim``)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_dim is None else self.v_dim
 
 
 @dataclass(frozen=True)
@@ -79,7 +85,7 @@ def is_paged(need) -> bool:
 def entry_elements(need) -> int:
     """Numbers a paged need stores per token."""
     if isinstance(need, KVNeed):
-        return 2 * need.num_kv_heads * need.head_dim
+        return need.num_kv_heads * (need.head_dim + need.value_dim)
     if isinstance(need, RowNeed):
         return need.width
     return 0

@@ -149,6 +149,123 @@ class ParallelResidualBlock:
         return residual, (y, z)
 
 
+class TokenSide:
+    """A second input per layer that depends on the token id alone: with ``e`` the layer's slice of the token's row of a
+    table shared by all layers (held by the embedding part, ``side_width`` wide), ``x`` the stream after the layer's
+    sub-layers and ``m`` the residual factor,
+
+        g = gelu_tanh(G x) * e;    y = P g;    x <- x + m * y / sqrt(mean(y^2) + eps) * w
+
+    params: ``hidden_size``, ``dim`` (the slice's size), ``offset`` (its first column in the table), ``eps``."""
+
+    graph_safe = True
+
+    def __init__(self, spec, dtype, device):
+        self.spec, self.dtype, self.device = spec, dtype, device
+        self.hidden = int(spec["hidden_size"])
+        self.dim = int(spec["dim"])
+        self.offset = int(spec["offset"])
+        self.eps = float(spec["eps"])
+        self.w_gate = self.w_proj = self.norm_w = None
+
+    def tensors(self):
+        from ..weights.loader import TensorSpec
+        return {"gate": TensorSpec((self.dim, self.hidden)), "proj": TensorSpec((self.hidden, self.dim)),
+                "norm": TensorSpec((self.hidden,), init="ones_jitter")}
+
+    def bind(self, tensors) -> None:
+        self.w_gate = tensors["gate"].contiguous()
+        self.w_proj = tensors["proj"].contiguous()
+        self.norm_w = tensors["norm"].to(torch.float32).contiguous()
+
+    def kernel_libraries(self):
+        return ("residual_ops", "gemm_simt")
+
+    def forward(self, residual: torch.Tensor, x_act: torch.Tensor, mult: float, ctx, rows: Optional[torch.Tensor]) -> None:
+        """Adds into ``residual`` in place.  ``x_act``: the stream in the activation dtype; ``rows``: the step's rows the
+        stream's rows stand for (None: all, in order)."""
+        table = ctx.step_cache.get("token_side_table")
+        if table is None:
+            raise RuntimeError("token_side: the embedding holds no second table (side_width)")
+        k = ops.kernels()
+        n = residual.shape[0]
+        g = ctx.buf("side_gate", (n, self.dim), self.dtype)
+        k.linear(x_act, self.w_gate, g)
+        ge = ctx.buf("side_gated", (n, self.dim), self.dtype)
+        k.gelu_mul_table(g, table, self.offset, ctx.tokens, rows, ge)
+        y = ctx.buf("side_out", (n, self.hidden), self.dtype)
+        k.linear(ge, self.w_proj, y)
+        k.scaled_add_unit_rms(residual, y, mult, self.norm_w, self.eps)
+
+
+@register_block("scaled_residual")
+class ScaledResidualBlock:
+    """``x += m mixer(norm1 x)``; ``x += m ffn(norm2 x)``; optionally ``x += m side(x, token)``: the pre-norm arrangement
+    with a factor ``m`` on everything that is added to the stream.
+
+    Slots: ``mixer_norm``, ``mixer``; optionally ``feed_forward`` with ``feed_forward_norm`` (a layer without one ends
+    after the mixer's sum); in ``extra``: ``residual_mult`` as ``PartSpec("constant", {"value": m})`` and optionally
+    ``token_side`` (:class:`TokenSide`).  The sum that closes a sub-layer rides in the norm kernel that opens the next
+    (``x += m d`` in float32, then the norm); the block's last sum leaves the stream complete, so it hands on no addend.
+    With ``select_rows`` (the run order's last entry) only the wanted rows go on after the mixer."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        if spec.slot("mixer") is None or spec.slot("mixer_norm") is None:
+            raise ValueError("arrangement scaled_residual needs the slots mixer, mixer_norm")
+        if (spec.slot("feed_forward") is None) != (spec.slot("feed_forward_norm") is None):
+            raise ValueError("arrangement scaled_residual: feed_forward and feed_forward_norm come together")
+        self.spec = spec
+        self.dtype = dtype
+        self.mixer_norm = NORMS.build(spec.mixer_norm, dtype, device)
+        self.mixer = MIXERS.build(spec.mixer, dtype, device)
+        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, dtype, device) if spec.feed_forward is not None else None
+        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, dtype, device) if spec.feed_forward is not None else None
+        m = spec.slot("residual_mult")
+        self.mult = float(m["value"]) if m is not None else 1.0
+        side = spec.slot("token_side")
+        self.token_side = TokenSide(side, dtype, device) if side is not None else None
+
+    def parts(self):
+        out = [("mixer_norm", self.mixer_norm), ("mixer", self.mixer)]
+        if self.feed_forward is not None:
+            out += [("feed_forward_norm", self.feed_forward_norm), ("feed_forward", self.feed_forward)]
+        if self.token_side is not None:
+            out.append(("token_side", self.token_side))
+        return tuple(out)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, residual: torch.Tensor, delta, ctx, cache, writes_cache: bool, select_rows: Optional[torch.Tensor]):
+        k = ops.kernels()
+        h = self.mixer_norm.forward(residual, delta, ctx)            # what the layer before left to add has no factor
+        y = self.mixer.forward(h, ctx, cache, writes_cache)
+        gathers = select_rows is not None and not getattr(ctx, "rows_identity", False)
+        rows = None
+        if gathers:
+            r = select_rows.shape[0]
+            res_sel = ctx.buf("residual_rows", (r, residual.shape[1]), residual.dtype)
+            y_sel = ctx.buf("mixer_out_rows", (r, y.shape[1]), y.dtype)
+            k.gather_rows(residual, select_rows, res_sel)
+            k.gather_rows(y, select_rows, y_sel)
+            residual, y, rows = res_sel, y_sel, select_rows
+        if self.feed_forward is not None:
+            h2 = self.feed_forward_norm.forward(residual, y, ctx, delta_scale=self.mult)
+            y = self.feed_forward.forward(h2, ctx)
+        # the block's last sum; the token side reads the finished stream
+        if self.token_side is None:
+            k.scaled_add_rms_norm(residual, y, self.mult, None, 0.0, None)
+            return residual, None
+        if self.dtype == torch.float32:
+            k.scaled_add_rms_norm(residual, y, self.mult, None, 0.0, None)
+            x_act = residual
+        else:
+            x_act = ctx.buf("stream_act", residual.shape, self.dtype)
+            k.scaled_add_rms_norm(residual, y, self.mult, None, 0.0, None, copy=x_act)
+        self.token_side.forward(residual, x_act, self.mult, ctx, rows)
+        return residual, None
+
+
 class SigmoidGate:
     """A gate of a sub-layer's output: ``sigmoid(W h + b)`` per element, ``h`` the sub-layer's input.  params: ``size``.
     The matrix rides as extra rows in the sub-layer's own first product (``stack_rows``); the bias and the sigmoid are

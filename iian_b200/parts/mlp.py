@@ -118,3 +118,46 @@ class GatedMLP(FeedForward):
         out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
         k.linear(act, self.w_down, out)
         return out
+
+
+@register_feed_forward("plain_mlp")
+class PlainMLP(FeedForward):
+    """A feed-forward without a gate: ``y = Wdown act(Wup h)``.
+
+    params: ``hidden_size``, ``intermediate_size``, ``activation``: ``xielu`` (two learned numbers p, q in a tensor of
+    their own: ``z > 0: softplus(p) z^2 + z / 2``, else ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2``); optional
+    ``names``: the local tensor names of (up, down, the activation's numbers)."""
+
+    def __init__(self, spec, dtype, device):
+        super().__init__(spec, dtype, device)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        act = spec.params.get("activation", "xielu")
+        if act != "xielu":
+            raise ValueError(f"plain_mlp: activation '{act}' has no kernel (xielu)")
+        self.activation = act
+        self.names = tuple(spec.params.get("names", ("up", "down", "act")))
+        self.w_up = self.w_down = self.act_numbers = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {self.names[0]: TensorSpec((self.inter, self.hidden)), self.names[1]: TensorSpec((self.hidden, self.inter)),
+                self.names[2]: TensorSpec((2,), init="zeros_jitter")}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_up = tensors[self.names[0]].contiguous()
+        self.w_down = tensors[self.names[1]].contiguous()
+        self.act_numbers = tensors[self.names[2]].to(torch.float32).contiguous()
+
+    def kernel_libraries(self):
+        return ("residual_ops", "gemm_simt")
+
+    def forward(self, x, ctx):
+        k = ops.kernels()
+        n = x.shape[0]
+        up = ctx.buf("ffn_up", (n, self.inter), self.dtype)
+        k.linear(x, self.w_up, up)
+        act = ctx.buf("ffn_act", (n, self.inter), self.dtype)
+        k.xielu(up, self.act_numbers, act)
+        out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
+        k.linear(act, self.w_down, out)
+        return out

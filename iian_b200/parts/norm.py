@@ -38,13 +38,20 @@ class RMSNorm(Norm):
         self.weight = (w + self.offset if self.offset else w).contiguous()
 
     def kernel_libraries(self):
-        return ("elementwise",)
+        return ("elementwise", "residual_ops")
 
     def foldable(self):
         return (self.weight, self.eps) if self.weight is not None else None
 
-    def forward(self, residual: torch.Tensor, delta, ctx) -> torch.Tensor:
+    def forward(self, residual: torch.Tensor, delta, ctx, delta_scale: float = 1.0) -> torch.Tensor:
+        """``delta_scale``: the stream becomes ``x + delta_scale * delta`` (a design that adds its sub-layers' outputs with a
+        factor)."""
         out = ctx.buf("normed", residual.shape, self.dtype)
+        if delta_scale != 1.0 and delta is not None:
+            if isinstance(delta, tuple):
+                raise ValueError("rms_norm: a pair of addends takes no factor")
+            ops.kernels().scaled_add_rms_norm(residual, delta, delta_scale, self.weight, self.eps, out)
+            return out
         if isinstance(delta, tuple):
             live = [d for d in delta if d is not None]
             if len(live) == 2:
