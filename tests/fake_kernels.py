@@ -289,10 +289,10 @@ class FakeKernels:
 
     # ---- attention over a cached latent ------------------------------------------------------------------
     def latent_prep(self, qd, q_off, dkv_off, cache_rows, q_cat, norm_weight, inv_freq, positions, slots, *, num_heads, dim,
-                    rot, rank, rot_dims, eps):
+                    rot, rank, rot_dims, eps, queries=None, style=0):
         n = qd.shape[0]
         x = qd.float()
-        q = x[:, q_off:q_off + num_heads * (dim + rot)].view(n, num_heads, dim + rot)
+        q = (x[:, q_off:q_off + num_heads * (dim + rot)] if queries is None else queries.float()).view(n, num_heads, dim + rot)
         dkv = x[:, dkv_off:dkv_off + rank + rot]
 
         def rope(t):
@@ -304,6 +304,11 @@ class FakeKernels:
             while cos.dim() < t.dim():
                 cos, sin = cos[:, None], sin[:, None]
             o = t.clone()
+            if style == 1:                      # neighbours are a pair
+                a, b = t[..., 0:rot_dims:2], t[..., 1:rot_dims:2]
+                o[..., 0:rot_dims:2] = a * cos - b * sin
+                o[..., 1:rot_dims:2] = a * sin + b * cos
+                return o
             a, b = t[..., :half], t[..., half:rot_dims]
             o[..., :half] = a * cos - b * sin
             o[..., half:rot_dims] = a * sin + b * cos
@@ -348,6 +353,119 @@ class FakeKernels:
                 sc = torch.cat([sc, sink[:, None]], dim=1)
             pr = torch.softmax(sc, dim=1)[:, : rows.shape[0]]
             out[t] = (pr @ rows[:, :rank]).to(out.dtype)
+
+    # ---- a stream whose addends carry a factor, a second per-token input, xIELU, the logit cap -------------
+    def scaled_add_rms_norm(self, residual, delta, mult, weight, eps, out, copy=None):
+        if delta is not None:
+            residual.add_(mult * delta.float())
+        if copy is not None:
+            copy.copy_(residual.to(copy.dtype))
+        if out is not None:
+            x = residual
+            out.copy_((x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
+
+    def scaled_add_unit_rms(self, residual, y, mult, weight, eps):
+        v = y.float()
+        residual.add_(mult * v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * weight)
+
+    def rms_norm_rows(self, x, weight, eps, out):
+        v = x.float()
+        out.copy_((v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
+
+    def gelu_mul_table(self, g, table, col_off, tokens, rows, out):
+        tok = tokens.long() if rows is None else tokens.long()[rows.long()]
+        e = table[tok[: g.shape[0]], col_off: col_off + g.shape[1]].float()
+        out.copy_((torch.nn.functional.gelu(g.float(), approximate="tanh") * e).to(out.dtype))
+
+    def xielu(self, x, pq, out):
+        z = x.float()
+        sp = torch.nn.functional.softplus
+        pos = sp(pq[0]) * z * z + 0.5 * z
+        zn = torch.clamp(z, max=0.0)
+        neg = (0.5 + sp(pq[1])) * (torch.expm1(zn) - zn) + 0.5 * z
+        out.copy_(torch.where(z > 0, pos, neg).to(out.dtype))
+
+    def tanh_cap(self, x, cap):
+        x.copy_(cap * torch.tanh(x / cap))
+
+    # ---- attention inside chunks of positions, with a penalty on distance ----------------------------------
+    def kv_store_normed(self, proj, k_off, v_off, k_cache, v_cache, slots, *, num_kv_heads, k_dim, v_dim, eps, norm_values):
+        n = proj.shape[0]
+        ps = k_cache.shape[2]
+        kk = proj[:, k_off:k_off + num_kv_heads * k_dim].view(n, num_kv_heads, k_dim)
+        vv = proj[:, v_off:v_off + num_kv_heads * v_dim].float().view(n, num_kv_heads, v_dim)
+        if norm_values:
+            vv = vv * torch.rsqrt((vv * vv).mean(-1, keepdim=True) + eps)
+        for t in range(n):
+            c = int(slots[t])
+            if c >= 0:
+                k_cache[c // ps, :, c % ps, :] = kk[t]
+                v_cache[c // ps, :, c % ps, :] = vv[t].to(v_cache.dtype)
+
+    def chunked_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, k_dim, v_dim, scale, chunk, window,
+                          r1, r2, gate):
+        n = q.shape[0]
+        ps = k_cache.shape[2]
+        rep = num_heads // num_kv_heads
+        qf = q.float().reshape(n, num_heads, k_dim)
+        o = torch.zeros(n, num_heads, v_dim)
+        for t in range(n):
+            s = int(meta.seq_of_token[t])
+            if s < 0:
+                continue
+            p = int(meta.positions[t])
+            lo = (p // chunk) * chunk if chunk else max(0, p - window + 1) if window else 0
+            js = torch.arange(lo, p + 1)
+            pages = meta.block_table[s, (js // ps).long()].long()
+            assert (pages >= 0).all(), "attention reads a page that was given back"
+            kk = k_cache[pages, :, (js % ps).long(), :].float()
+            vv = v_cache[pages, :, (js % ps).long(), :].float()
+            for h in range(num_heads):
+                sc = (kk[:, h // rep, :] @ qf[t, h]) * scale
+                if r1 is not None:
+                    sc = sc - r1[h] * torch.log1p(r2[h] * (p - js).float())
+                o[t, h] = torch.softmax(sc, dim=0) @ vv[:, h // rep, :]
+        o = o.view(n, num_heads * v_dim)
+        if gate is not None:
+            o = o * torch.sigmoid(gate.float())
+        out.copy_(o.to(out.dtype))
+
+    # ---- the delta rule with a decay per key channel --------------------------------------------------------
+    def delta_rule(self, proj, col_off, b_off, z, taps, a_log, dt_bias, state, ctx, out, *, num_heads, num_kv_heads, dim, v_dim):
+        H, G, D, V = num_heads, num_kv_heads, dim, v_dim
+        C = 2 * G * D + H * V
+        n_taps = taps.shape[1]
+        back = n_taps - 1
+        cu_q, slots = ctx.cu_q, ctx.state_slots
+        sp = torch.nn.functional.softplus
+        for s in range(slots.numel()):
+            t0, t1, slot = int(cu_q[s]), int(cu_q[s + 1]), int(slots[s])
+            if slot < 0:
+                out[t0:t1] = 0
+                continue
+            if t1 <= t0:
+                continue
+            st = state[slot]
+            S = st[: H * V * D].view(H, V, D).clone()                   # a column of S is contiguous
+            tail = st[H * V * D:].view(back, C).clone()
+            ext = torch.cat([tail, proj[t0:t1, col_off:col_off + C].float()], dim=0)
+            for i, t in enumerate(range(t0, t1)):
+                x = (ext[i: i + n_taps] * taps.T).sum(0)                # the last tap multiplies the token's own row
+                a = x * torch.sigmoid(x)
+                q = a[: G * D].view(G, D)
+                k = a[G * D: 2 * G * D].view(G, D)
+                q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * D ** -0.5
+                k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+                q, k = q.repeat_interleave(H // G, dim=0), k.repeat_interleave(H // G, dim=0)
+                v = a[2 * G * D:].view(H, V)
+                beta = torch.sigmoid(proj[t, b_off:b_off + H].float())
+                g = torch.exp(-torch.exp(a_log)[:, None] * sp(z[t].view(H, D) + dt_bias.view(H, D)))
+                S = S * g[:, None, :]
+                u = beta[:, None] * (v - torch.einsum("hvd,hd->hv", S, k))
+                S = S + u[:, :, None] * k[:, None, :]
+                out[t] = torch.einsum("hvd,hd->hv", S, q).reshape(-1)
+            st[: H * V * D] = S.reshape(-1)
+            st[H * V * D:] = ext[ext.shape[0] - back:].reshape(-1)
 
     # ---- routed experts ----------------------------------------------------------------------------------
     def moe_tile_rows(self):

@@ -233,7 +233,7 @@ def forward(cfg: Mapping, tensors: Mapping[str, torch.Tensor], tokens, dtype=tor
     t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
     tok = torch.as_tensor(tokens, dtype=torch.long)
     eps = cfg["norm"]["eps"]
-    m = cfg["residual_mult"]
+    m = cfg.get("residual_mult", 1.0)
     x = t["embed"][tok]
     side = cfg.get("token_side")
     kept: Dict[int, tuple] = {}
@@ -264,7 +264,9 @@ def forward(cfg: Mapping, tensors: Mapping[str, torch.Tensor], tokens, dtype=tor
             e = t["side.embed"][tok][:, i * d: (i + 1) * d]
             x = x + m * token_side(x, e, t, pre + "side.", eps)
         layers.append(x)
-    logits = tanh_cap(mm(rms_norm(x, t["final.norm"], eps), t["head"]), cfg["logit_softcap"])
+    logits = mm(rms_norm(x, t["final.norm"], eps), t["head"])
+    if cfg.get("logit_softcap") is not None:
+        logits = tanh_cap(logits, cfg["logit_softcap"])
     if return_layers:
         return logits, torch.stack(layers)
     return logits
