@@ -409,6 +409,179 @@ def run_lekilix(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
     return out
 
 
+def run_senadra(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
+    """The kernels of the Senadra design alone, each beside its like kernel of another path at equal size (16 heads of 128 on
+    8 KV heads, chunks of 2,048 positions; recurrences of 16 value heads 128 x 128 on 8 query/key heads; latents of 512 + 64):
+      decode attention    8 (and 64) sequences of 4,096 cached tokens, 2,048 of them in the query's chunk: chunked with the
+                          distance penalty and the gate  vs  the Qwen3 kernel with a window of 2,048     bytes of cache read
+      prefill attention   one sequence of 2,048 tokens (one chunk)  vs  the Qwen3 kernel                 flops of scores and values
+      cache write         2,048 tokens: keys, values over their root mean square  vs  per-head norm, rotation, cache write
+      sum + norm          2,048 rows: the sum with a factor  vs  the plain sum; the normalised addend (no like kernel)
+      feed-forward        2,048 (and 8) rows: up, xIELU, down  vs  gate/up with SwiGLU, down, of equal weights
+      delta-rule scan     8 / 64 sequences of one token (bytes of state) and one sequence of 2,048 tokens  vs  the
+                          matrix-memory scan of equal state (8 heads 128 x 256)
+    """
+    import torch
+    from .. import ops
+    from ..parts.matrix_memory import state_block_floats, state_columns
+    k = ops.kernels()
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    nkv, hd, page, chunk = 8, 128, 16, 2048
+    out = {}
+    hbm, tfl = peaks["hbm_gbs"], peaks["bf16_tflops"]
+
+    def mem_row(name, ms, nbytes):
+        out[name] = {"ms": ms, "gb_s": nbytes / ms / 1e6, "of_hbm_peak": nbytes / ms / 1e6 / hbm}
+
+    def flop_row(name, ms, flops):
+        out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "of_bf16_peak": flops / ms / 1e9 / tfl}
+
+    r1 = torch.rand(heads, device=dev) * 0.3
+    r2 = torch.rand(heads, device=dev) + 0.5
+    # ---- decode attention ------------------------------------------------------------------------------------------------
+    for B, ctx in ((8, 4096), (64, 4096)):
+        meta, pages = _meta([ctx] * B, [1] * B, page, dev)
+        copies = [(torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3, torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3)
+                  for _ in range(3 if B == 8 else 2)]
+        q = torch.randn(B, heads * hd, device=dev).to(bf) * 0.1
+        gate = torch.randn(B, heads * hd, device=dev).to(bf)
+        o = torch.empty(B, heads * hd, device=dev, dtype=bf)
+        nbytes = B * (ctx - chunk) * 2 * nkv * hd * 2
+        ms = _timed([(lambda c=c: k.chunked_attention(q, c[0], c[1], o, meta, num_heads=heads, num_kv_heads=nkv, k_dim=hd, v_dim=hd,
+                                                      scale=0.088, chunk=chunk, window=None, r1=r1, r2=r2, gate=gate)) for c in copies])
+        mem_row(f"decode_attention_chunked_{B}x{ctx}", ms, nbytes)
+        q3 = q.view(B, heads, hd)
+        ms = _timed([(lambda c=c: k.paged_attention(q3, c[0], c[1], o, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088,
+                                                    window=chunk)) for c in copies])
+        mem_row(f"decode_attention_qwen3_{B}x{ctx}", ms, nbytes)
+        del copies
+    torch.cuda.empty_cache()
+    # ---- prefill attention -----------------------------------------------------------------------------------------------
+    T = 2048
+    meta, pages = _meta([T], [T], page, dev)
+    kc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+    vc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+    q = torch.randn(T, heads * hd, device=dev).to(bf) * 0.1
+    gate = torch.randn(T, heads * hd, device=dev).to(bf)
+    o = torch.empty(T, heads * hd, device=dev, dtype=bf)
+    pairs = T * (T + 1) / 2
+    ms = _timed([lambda: k.chunked_attention(q, kc, vc, o, meta, num_heads=heads, num_kv_heads=nkv, k_dim=hd, v_dim=hd, scale=0.088,
+                                             chunk=chunk, window=None, r1=r1, r2=r2, gate=gate)] * 4)
+    flop_row("prefill_attention_chunked", ms, 4.0 * heads * hd * pairs)
+    q3 = q.view(T, heads, hd)
+    ms = _timed([lambda: k.paged_attention(q3, kc, vc, o, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088, window=None)] * 4)
+    flop_row("prefill_attention_qwen3", ms, 4.0 * heads * hd * pairs)
+    # ---- cache write -----------------------------------------------------------------------------------------------------
+    slots = torch.arange(T, dtype=torch.int32, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    front = 2 * heads * hd
+    sets = [(torch.randn(T, front + 2 * nkv * hd, device=dev).to(bf), torch.zeros_like(kc), torch.zeros_like(vc)) for _ in range(4)]
+    ms = _timed([(lambda t=t: k.kv_store_normed(t[0], front, front + nkv * hd, t[1], t[2], slots, num_kv_heads=nkv, k_dim=hd, v_dim=hd,
+                                                eps=1e-6, norm_values=True)) for t in sets])
+    mem_row("kv_store_normed", ms, 2 * T * 2 * nkv * hd * 2)
+    sets2 = [(torch.randn(T, (heads + 2 * nkv) * hd, device=dev).to(bf), torch.empty(T, heads, hd, device=dev, dtype=bf), t[1], t[2])
+             for t in sets]
+    qw2, kw2 = torch.ones(hd, device=dev), torch.ones(hd, device=dev)
+    inv_full = torch.pow(torch.tensor(500000.0), -torch.arange(hd // 2, dtype=torch.float32) / (hd // 2)).to(dev)
+    ms = _timed([(lambda t=t: k.qk_norm_rope_store(t[0], t[1], t[2], t[3], num_heads=heads, num_kv_heads=nkv, head_dim=hd, q_weight=qw2,
+                                                   k_weight=kw2, eps=1e-6, inv_freq=inv_full, rot_dim=hd, rope_style=0, positions=pos,
+                                                   slots=slots, write_kv=True)) for t in sets2])
+    mem_row("qk_norm_rope_store_qwen3", ms, 2 * T * (heads + 2 * nkv) * hd * 2)
+    del sets, sets2, kc, vc
+    # ---- sums and norms ---------------------------------------------------------------------------------------------------
+    n = 2048
+    w = torch.ones(width, device=dev)
+    sets = [(torch.randn(n, width, device=dev), torch.randn(n, width, device=dev).to(bf), torch.empty(n, width, device=dev, dtype=bf))
+            for _ in range(8)]
+    ms = _timed([(lambda t=t: k.scaled_add_rms_norm(t[0], t[1], 0.5, w, 1e-6, t[2])) for t in sets])
+    mem_row("scaled_add_rms_norm", ms, n * width * (4 + 2 + 4 + 2))
+    ms = _timed([(lambda t=t: k.add_rms_norm(t[0], t[1], w, 1e-6, t[2])) for t in sets])
+    mem_row("add_rms_norm_qwen3", ms, n * width * (4 + 2 + 4 + 2))
+    ms = _timed([(lambda t=t: k.scaled_add_unit_rms(t[0], t[1], 0.5, w, 1e-6)) for t in sets])
+    mem_row("scaled_add_unit_rms", ms, n * width * (4 + 2 + 4))
+    del sets
+    # ---- feed-forward: ungated with xIELU beside gated with SwiGLU, equal weights -------------------------------------------
+    from ..config.spec import PartSpec
+    from ..engine.runner import StepContext, Workspace
+    from ..parts.mlp import PlainMLP
+    inter = 4 * width
+    for n in (2048, 8):
+        h = torch.randn(n, width, device=dev).to(bf)
+        reps = 3 if n < 128 else 1
+        plain_parts = []
+        for _ in range(reps):
+            part = PlainMLP(PartSpec("plain_mlp", {"hidden_size": width, "intermediate_size": inter * 3 // 2, "activation": "xielu"}), bf, dev)
+            part.bind({"up": torch.randn(inter * 3 // 2, width, device=dev).to(bf) * 0.02,
+                       "down": torch.randn(width, inter * 3 // 2, device=dev).to(bf) * 0.02, "act": torch.tensor([0.3, -0.2], device=dev)})
+            plain_parts.append(part)
+        ctx_ = StepContext(Workspace(dev))
+        ms = _timed([(lambda p_=p_: p_.forward(h, ctx_)) for p_ in plain_parts] * (1 if n < 128 else 3))
+        wgus = [torch.randn(2 * inter, width, device=dev).to(bf) * 0.02 for _ in range(reps)]
+        wds = [torch.randn(width, inter, device=dev).to(bf) * 0.02 for _ in range(reps)]
+        a2, y2 = torch.empty(n, inter, device=dev, dtype=bf), torch.empty(n, width, device=dev, dtype=bf)
+        gu = torch.empty(n, 2 * inter, device=dev, dtype=bf)
+        fused = k.can_fuse_swiglu(h, wgus[0], 8)
+
+        def dense_on(wa, wb):
+            def run_():
+                if fused:
+                    k.linear_swiglu(h, wa, a2)
+                else:
+                    k.linear(h, wa, gu)
+                    k.swiglu(gu, a2, 8)
+                k.linear(a2, wb, y2)
+            return run_
+        ms_dense = _timed([dense_on(a, b) for a, b in zip(wgus, wds)] * (1 if n < 128 else 3))
+        if n >= 128:
+            flop_row(f"xielu_feed_forward_{n}", ms, 2.0 * n * 3 * inter * width)
+            flop_row(f"swiglu_feed_forward_{n}", ms_dense, 2.0 * n * 3 * inter * width)
+        else:
+            mem_row(f"xielu_feed_forward_{n}", ms, 3 * inter * width * 2)
+            mem_row(f"swiglu_feed_forward_{n}", ms_dense, 3 * inter * width * 2)
+        del plain_parts, wgus, wds
+    torch.cuda.empty_cache()
+    # ---- the delta-rule scan beside the matrix-memory scan of equal state ------------------------------------------------------
+    H, G, d, dv, taps = heads, heads // 2, 128, 128, 4
+    channels = 2 * G * d + H * dv
+    conv_w = torch.randn(channels, taps, device=dev) * 0.3
+    a_log, dt_bias = torch.zeros(H, device=dev), torch.zeros(H * d, device=dev)
+    n_state = k.delta_state_floats(H, G, d, dv, taps)
+    ws = Workspace(dev)
+    for B, L in ((8, 1), (64, 1), (1, 2048)):
+        n = B * L
+        sets = [(torch.randn(n, channels + H, device=dev).to(bf) * 0.5, torch.randn(n, H * d, device=dev),
+                 torch.zeros(B, n_state, device=dev), torch.empty(n, H * dv, device=dev)) for _ in range(4 if L == 1 else 1)]
+        sc = StepContext(ws)
+        sc.cu_q = torch.arange(0, n + 1, L, dtype=torch.int32, device=dev)
+        sc.state_slots = torch.arange(B, dtype=torch.int32, device=dev)
+        sc.seq_of_token = torch.arange(n, dtype=torch.int32, device=dev) // L
+        ms = _timed([(lambda t=t: k.delta_rule(t[0], 0, channels, t[1], conv_w, a_log, dt_bias, t[2], sc, t[3], num_heads=H,
+                                               num_kv_heads=G, dim=d, v_dim=dv)) for t in sets])
+        if L == 1:
+            mem_row(f"delta_rule_decode_{B}", ms, B * 2 * H * d * dv * 4)
+        else:
+            flop_row(f"delta_rule_prefill_{L}", ms, 6.0 * L * H * d * dv)
+        del sets
+        Hm, dm, dvm, cap = heads // 2, 128, 256, 15.0
+        cb = state_columns(dm, dvm)
+        wide = 2 * Hm * dm + 2 * Hm * dvm
+        bias = torch.zeros(2 * Hm, device=dev)
+        sets = [(torch.randn(n, wide, device=dev).to(bf) * 0.5, torch.randn(n, 2 * Hm, device=dev),
+                 torch.zeros(B, Hm, dvm // cb, state_block_floats(dm, cb), device=dev), torch.empty(n, Hm * dvm, device=dev))
+                for _ in range(4 if L == 1 else 1)]
+        ms = _timed([(lambda t=t: k.matrix_memory_scan(t[0], 0, Hm * dm, 2 * Hm * dm, t[1], bias, t[2], sc.cu_q, sc.state_slots, t[3],
+                                                       num_heads=Hm, dim=dm, v_dim=dvm, columns=cb, cap=cap, q_scale=dm ** -0.5,
+                                                       max_q_len=L)) for t in sets])
+        if L == 1:
+            mem_row(f"memory_scan_decode_{B}", ms, B * 2 * Hm * (dm * dvm + dm) * 4)
+        else:
+            flop_row(f"memory_scan_prefill_{L}", ms, 4.0 * L * Hm * dm * (dvm + 1))
+        del sets
+    k.check_device_status()
+    return out
+
+
 def main(argv=None) -> int:
     from . import workloads
     peaks, kind = workloads.load_peaks()

@@ -89,7 +89,35 @@ LEKILIX_SHAPES: Dict[str, dict] = {
 }
 EQUAL_QWEN3.update({"l2k-dense": _qwen3_shape(2048, 16, 8, 8192), "l2k-moe": _qwen3_shape(2048, 16, 8, 6 * 1408),
                     "l4k-dense": _qwen3_shape(4096, 32, 8, 12288)})
-DESIGN_SHAPES = {"galodra": GALODRA_SHAPES, "lekilix": LEKILIX_SHAPES}
+
+
+def _senadra_shape(width, heads, ff, vocab=32768, chunk=2048):
+    """Eight layers -- chunked attention, delta rule, latent attention, a reader of the first layer's keys and values, delta
+    rule, latent attention, chunked attention, delta rule: attention heads of 128 on 8 key/value heads; recurrences of as many
+    value heads 128 wide on half as many query/key heads 128 deep, four taps; latents of 512 + 64 rotated behind a query
+    latent of 1,536; a second per-token input of 256 per layer; an ungated feed-forward 1.5 times as wide as the gated one
+    of the Qwen3 shape beside it (equal weights)."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                          "mask": {"size": chunk}}}
+    reader = {"type": "attention", "mixer": dict(att["mixer"], kv_from=0)}
+    rec = {"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4,
+                                              "decay_rank": 64, "gate_rank": 64}}
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512,
+                                                 "q_rank": 1536, "scale": 192 ** -0.5, "rot": {"dims": 64, "base": 10000.0}}}
+    order = [att, rec, lat, reader, rec, lat, att, rec]
+    return {"architecture": "Senadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "token_side": {"dim": 256}, "logit_softcap": 30.0,
+            "layers": [dict(type=l["type"], mixer=dict(l["mixer"]), mlp={"kind": "dense", "ff": ff}) for l in order]}
+
+
+# Senadra shapes with layer sizes of real models, and beside each the Qwen3 dense shape of equal width, heads, layers and
+# feed-forward weights.
+SENADRA_SHAPES: Dict[str, dict] = {
+    "s2k": _senadra_shape(2048, 16, 12288),
+    "s4k": _senadra_shape(4096, 32, 18432),
+}
+EQUAL_QWEN3.update({"s2k": _qwen3_shape(2048, 16, 8, 8192), "s4k": _qwen3_shape(4096, 32, 8, 12288)})
+DESIGN_SHAPES = {"galodra": GALODRA_SHAPES, "lekilix": LEKILIX_SHAPES, "senadra": SENADRA_SHAPES}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -124,10 +152,17 @@ def shape_config(name: str, layers: Optional[int] = None):
             raw["layers"] = raw["layers"][:layers]
             raw["loop"] = None if layers < raw["loop"]["stop"] else raw["loop"]
         return lekilix_config_from_dict(raw)
+    if name in SENADRA_SHAPES:
+        from ..models.senadra import senadra_config_from_dict
+        raw = dict(SENADRA_SHAPES[name])
+        if layers:
+            raw["layers"] = raw["layers"][:layers]
+        return senadra_config_from_dict(raw)
     try:
         raw = dict(SHAPES[name])
     except KeyError:
-        raise ValueError(f"unknown shape '{name}' ({' | '.join(list(SHAPES) + list(GALODRA_SHAPES) + list(LEKILIX_SHAPES))})") from None
+        known = list(SHAPES) + list(GALODRA_SHAPES) + list(LEKILIX_SHAPES) + list(SENADRA_SHAPES)
+        raise ValueError(f"unknown shape '{name}' ({' | '.join(known)})") from None
     if layers:
         raw["num_hidden_layers"] = layers
     return qwen3_config_from_dict(raw)
@@ -138,7 +173,8 @@ def random_model(name: str, dtype: str = "bfloat16", device="cuda:0", seed: int 
     from ..config.registry import get_architecture
     from ..engine.model import Model
     cfg = shape_config(name, layers)
-    arch = "Galodra" if name in GALODRA_SHAPES else "Lekilix" if name in LEKILIX_SHAPES else "Qwen3ForCausalLM"
+    arch = ("Galodra" if name in GALODRA_SHAPES else "Lekilix" if name in LEKILIX_SHAPES else "Senadra" if name in SENADRA_SHAPES
+            else "Qwen3ForCausalLM")
     return Model.from_random(get_architecture(arch), cfg, seed=seed, dtype=dtype, device=device, norm_jitter=0.0)
 
 
@@ -146,6 +182,8 @@ def accounting_for(cfg, dtype_bytes: int = 2):
     """Bytes and flops of a step for a configuration of any built-in architecture."""
     if hasattr(cfg, "embedding_scale"):
         return LekilixAccounting(cfg, dtype_bytes)
+    if hasattr(cfg, "residual_mult"):
+        return SenadraAccounting(cfg, dtype_bytes)
     return GalodraAccounting(cfg, dtype_bytes) if hasattr(cfg, "postln_alpha") else Accounting(cfg, dtype_bytes)
 
 
@@ -263,6 +301,63 @@ class LekilixAccounting:
                 total += 4.0 * m.heads * m.dim * pairs
             else:
                 total += 4.0 * tokens * m.heads * m.dim * (m.vdim + 1)         # the update and the read-out of every token
+        return total
+
+
+class SenadraAccounting:
+    """Bytes and flops of a Senadra step.  A decode step reads every weight once, of a chunked layer's K/V cache the cells of
+    the query's chunk, of a latent cache every row, and reads and writes every recurrence's float32 state; of the second
+    embedding table a token reads one row."""
+
+    def __init__(self, cfg, dtype_bytes: int = 2):
+        self.cfg, self.b = cfg, dtype_bytes
+        self.head_w = cfg.vocab * cfg.width
+
+    def _layer(self, lc) -> float:
+        """Weights of one layer."""
+        w, m = self.cfg.width, lc.mixer
+        if lc.type == "attention":
+            mix = w * (m.heads * m.dim + m.heads * m.vdim) + m.heads * m.vdim * w
+            if m.kv_from is None:
+                mix += w * m.kv_heads * (m.dim + m.vdim)
+        elif lc.type == "latent_attention":
+            q = w * m.q_rank + m.q_rank * m.heads * (m.dim + m.rot_dim) if m.q_rank else w * m.heads * (m.dim + m.rot_dim)
+            mix = q + w * (m.kv_rank + m.rot_dim) + m.heads * (m.dim + m.vdim) * m.kv_rank + 2 * w * m.heads * m.vdim
+        else:
+            mix = w * (2 * m.kv_heads * m.dim + m.heads * m.vdim + m.heads) + w * (m.decay_rank + m.gate_rank) \
+                + m.decay_rank * m.heads * m.dim + m.gate_rank * m.heads * m.vdim + m.heads * m.vdim * w
+        if lc.mlp is not None:
+            mix += 2 * w * lc.mlp.ff
+        return mix + 2 * w * self.cfg.side_dim
+
+    def decode_bytes(self, batch: int, ctx_avg: float) -> float:
+        total = self.head_w * self.b
+        for lc in self.cfg.layers:
+            total += self._layer(lc) * self.b
+            m = lc.mixer
+            if lc.type == "attention":
+                keys = min(ctx_avg, (m.chunk + 1) / 2) if m.chunk else ctx_avg
+                total += batch * keys * m.kv_heads * (m.dim + m.vdim) * self.b
+            elif lc.type == "latent_attention":
+                total += batch * ctx_avg * (m.kv_rank + m.rot_dim) * self.b
+            else:
+                total += batch * 2 * m.heads * m.dim * m.vdim * 4
+        return total
+
+    def prefill_flops(self, tokens: int) -> float:
+        total = 2.0 * self.head_w
+        for lc in self.cfg.layers:
+            m = lc.mixer
+            total += 2.0 * tokens * self._layer(lc)
+            if lc.type == "attention":
+                c = m.chunk or tokens
+                full, rest = divmod(tokens, c)
+                pairs = full * c * (c + 1) / 2 + rest * (rest + 1) / 2
+                total += 2.0 * m.heads * (m.dim + m.vdim) * pairs
+            elif lc.type == "latent_attention":
+                total += 2.0 * m.heads * (2 * m.kv_rank + m.rot_dim) * tokens * (tokens + 1) / 2
+            else:
+                total += 6.0 * tokens * m.heads * m.dim * m.vdim          # S^T k, the update and the read-out of every token
         return total
 
 

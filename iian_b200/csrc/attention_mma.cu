@@ -54,7 +54,28 @@ struct AttnParams {
     // a sink per head: a logit without key and value that joins the softmax's denominator once, not scaled
     const float * sink = nullptr;   // [nh] or null
     float sink_to_raw = 0.0f;       // 1 / scale: the kernels keep maxima of raw scores and scale in the exponent
+    long long ld_q = 0;             // elements between the rows of q (nh * HD when q is contiguous)
+    // chunked mask: key j is visible to position i only if floor(i / chunk) == floor(j / chunk) (0: no chunks)
+    int chunk = 0;
+    // a penalty on distance, taken off the scaled score: pen1[h] * ln(1 + pen2[h] * (i - j)); null: none
+    const float * pen1 = nullptr;   // [nh]
+    const float * pen2 = nullptr;   // [nh]
+    float pen_to_raw = 0.0f;        // 1 / scale_log2: pen1 * log2(1 + pen2 d) in units of raw scores
+    // the output times sigmoid(gate): rows of nh * HD with ld_gate elements between them; null: none
+    const __nv_bfloat16 * gate = nullptr;
+    long long ld_gate = 0;
 };
+
+// first key of the chunk that position `pos` lies in
+__device__ __forceinline__ int chunk_start(int pos, int chunk) { return chunk > 0 ? pos - pos % chunk : 0; }
+// the gate's factor for two neighbouring output columns of row (token, head): sigmoid in float32
+__device__ __forceinline__ float2 gate_pair(const AttnParams & p, size_t token, int col) {
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p.gate + token * p.ld_gate + col));
+    return make_float2(1.0f / (1.0f + __expf(-g.x)), 1.0f / (1.0f + __expf(-g.y)));
+}
+__device__ __forceinline__ float gate_one(const AttnParams & p, size_t token, int col) {
+    return 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[token * p.ld_gate + col])));
+}
 
 // Tensor maps of the K and V caches for the TMA form of the decode kernel (unused by the other forms).
 struct KvMaps {
@@ -159,7 +180,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
     const int tok_min = row0 / G;
     const int tok_max = min(rows_total - 1, row0 + BM - 1) / G;
     const int k_hi = pos0 + tok_max;
-    const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : 0;
+    const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : chunk_start(pos0 + tok_min, p.chunk);
     const int tile_lo = k_lo / BN, tile_hi = k_hi / BN;
     const int n_tiles = tile_hi - tile_lo + 1;
     const int per = (n_tiles + p.n_split - 1) / p.n_split;
@@ -175,7 +196,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
             const int R = row0 + r;
             const bool valid = R < rows_total;
             const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
-            const __nv_bfloat16 * src = p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8;
+            const __nv_bfloat16 * src = p.q + (size_t) (q0 + tok) * p.ld_q + (size_t) head * HD + ch * 8;
             cp_async16(smem_u32(sQ + swz<HD>(r, ch)), src, valid);
         }
     };
@@ -214,12 +235,18 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
 
     // rows of this thread: warp * 16 + g_ and + 8
-    int row_tok[2], row_ok[2];
+    int row_tok[2], row_ok[2], row_lo[2];
+    float pen_a[2] = {0.0f, 0.0f}, pen_b[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const int R = row0 + warp * 16 + g_ + 8 * h;
         row_ok[h] = R < rows_total;
         row_tok[h] = pos0 + (row_ok[h] ? R / G : 0);       // position of the row's token
+        row_lo[h] = chunk_start(row_tok[h], p.chunk);      // first key of its chunk
+        if (p.pen1 != nullptr && row_ok[h]) {
+            pen_a[h] = p.pen1[kvh * G + R % G] * p.pen_to_raw;
+            pen_b[h] = p.pen2[kvh * G + R % G];
+        }
     }
     if (p.sink != nullptr && split == 0) {
         // the running softmax of a row starts at the sink: maximum sink, sum 1 (the sum is kept in parts over the quad)
@@ -236,6 +263,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
     const int wr0 = row0 + warp * 16, wr1 = min(rows_total - 1, wr0 + 15);
     const bool warp_rows_ok = wr0 + 15 < rows_total;
     const int warp_pos_min = pos0 + min(wr0, rows_total - 1) / G, warp_pos_max = pos0 + max(wr1, 0) / G;
+    const int warp_lo_max = chunk_start(warp_pos_max, p.chunk);      // keys below it are outside some row's chunk
 
     if (tile_begin < tile_end) {
         lookup_rows(tile_begin, 0);
@@ -289,8 +317,19 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
             }
             // ---- mask (only on tiles that touch a row's causal or window edge), online softmax ----
             const int key0 = tile * BN;
+            if (p.pen1 != nullptr) {                        // the distance penalty, in units of raw scores
+#pragma unroll
+                for (int nt = 0; nt < BN / 8; nt++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int h = e >> 1;
+                        const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
+                        sc[nt][e] = fmaf(-pen_a[h], __log2f(fmaf(pen_b[h], (float) (row_tok[h] - j), 1.0f)), sc[nt][e]);
+                    }
+                }
+            }
             const bool need_mask = key0 + BN - 1 > warp_pos_min || !warp_rows_ok ||
-                                   (p.window > 0 && warp_pos_max - key0 >= p.window);
+                                   (p.window > 0 && warp_pos_max - key0 >= p.window) || key0 < warp_lo_max;
             if (need_mask) {
 #pragma unroll
                 for (int nt = 0; nt < BN / 8; nt++) {
@@ -298,7 +337,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
                     for (int e = 0; e < 4; e++) {
                         const int h = e >> 1;
                         const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window);
+                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window) && j >= row_lo[h];
                         if (!vis) sc[nt][e] = -INFINITY;
                     }
                 }
@@ -382,7 +421,12 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
 #pragma unroll
             for (int dt = 0; dt < DT; dt++) {
                 const int d = dt * 8 + 2 * t_;
-                *reinterpret_cast<__nv_bfloat162 *>(dst + d) = __floats2bfloat162_rn(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+                float2 v = make_float2(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+                if (p.gate != nullptr) {
+                    const float2 gt = gate_pair(p, (size_t) (q0 + tok), head * HD + d);
+                    v.x *= gt.x; v.y *= gt.y;
+                }
+                *reinterpret_cast<__nv_bfloat162 *>(dst + d) = __floats2bfloat162_rn(v.x, v.y);
             }
         } else {
             float * dst = p.part_o + (row_idx * p.n_split + split) * HD;
@@ -454,7 +498,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
     const int tok_min = row0 / G;
     const int tok_max = min(rows_total - 1, row0 + BM - 1) / G;
     const int k_hi = pos0 + tok_max;
-    const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : 0;
+    const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : chunk_start(pos0 + tok_min, p.chunk);
     const int tile_lo = k_lo / BN, tile_hi = k_hi / BN;
     const int n_tiles = tile_hi - tile_lo + 1;
     const int per = (n_tiles + p.n_split - 1) / p.n_split;
@@ -549,12 +593,18 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
 #pragma unroll
     for (int i = 0; i < DT; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-    int row_tok[2], row_ok[2];
+    int row_tok[2], row_ok[2], row_lo[2];
+    float pen_a[2] = {0.0f, 0.0f}, pen_b[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         const int R = row0 + g_ + 8 * h;
         row_ok[h] = R < rows_total;
         row_tok[h] = pos0 + (row_ok[h] ? R / G : 0);
+        row_lo[h] = chunk_start(row_tok[h], p.chunk);
+        if (p.pen1 != nullptr && row_ok[h]) {
+            pen_a[h] = p.pen1[kvh * G + R % G] * p.pen_to_raw;
+            pen_b[h] = p.pen2[kvh * G + R % G];
+        }
     }
     if (p.sink != nullptr && split == 0 && warp == 0) {
         // the sink counts once: in the first warp of the first part (the merges weigh it like any other part)
@@ -568,6 +618,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
         }
     }
     const int pos_min = pos0 + tok_min, pos_max = pos0 + tok_max;
+    const int lo_max = chunk_start(pos_max, p.chunk);
     const bool rows_full = row0 + BM <= rows_total;
 
     // Everything up to here reads only the step's integer buffers, which were uploaded before the first
@@ -589,7 +640,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
                 const int R = row0 + r;
                 const bool valid = R < rows_total;
                 const int tok = valid ? R / G : 0, head = kvh * G + (valid ? R % G : 0);
-                cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + ((size_t) (q0 + tok) * p.nh + head) * HD + ch * 8, valid);
+                cp_async16(smem_u32(sQ + swz<HD>(r, ch)), p.q + (size_t) (q0 + tok) * p.ld_q + (size_t) head * HD + ch * 8, valid);
             }
             load_ahead();
         } else {
@@ -716,7 +767,18 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
                 mma16816(sc[1], qf[ks], b2, b3);
             }
             const int key0 = (tile_begin + i) * BN + warp * 16;
-            const bool need_mask = key0 + 15 > pos_min || !rows_full || (p.window > 0 && pos_max - key0 >= p.window);
+            if (p.pen1 != nullptr) {                        // the distance penalty, in units of raw scores
+#pragma unroll
+                for (int nt = 0; nt < 2; nt++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int h = e >> 1;
+                        const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
+                        sc[nt][e] = fmaf(-pen_a[h], __log2f(fmaf(pen_b[h], (float) (row_tok[h] - j), 1.0f)), sc[nt][e]);
+                    }
+                }
+            }
+            const bool need_mask = key0 + 15 > pos_min || !rows_full || (p.window > 0 && pos_max - key0 >= p.window) || key0 < lo_max;
             if (need_mask) {
 #pragma unroll
                 for (int nt = 0; nt < 2; nt++) {
@@ -724,7 +786,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
                     for (int e = 0; e < 4; e++) {
                         const int h = e >> 1;
                         const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window);
+                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window) && j >= row_lo[h];
                         if (!vis) sc[nt][e] = -INFINITY;
                     }
                 }
@@ -842,9 +904,11 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
             }
             if (CLUSTER)
                 *reinterpret_cast<float2 *>(cO + mr * HD + d) = make_float2(v0, v1);
-            else if (p.n_split == 1)
-                *reinterpret_cast<__nv_bfloat162 *>(p.out + row_idx * HD + d) = __floats2bfloat162_rn(v0 * inv, v1 * inv);
-            else
+            else if (p.n_split == 1) {
+                float2 gt = make_float2(1.0f, 1.0f);
+                if (p.gate != nullptr) gt = gate_pair(p, (size_t) (q0 + mR / G), (kvh * G + mR % G) * HD + d);
+                *reinterpret_cast<__nv_bfloat162 *>(p.out + row_idx * HD + d) = __floats2bfloat162_rn(v0 * inv * gt.x, v1 * inv * gt.y);
+            } else
                 *reinterpret_cast<float2 *>(p.part_o + (row_idx * p.n_split + split) * HD + d) = make_float2(v0 * inv, v1 * inv);
         }
         if (CLUSTER) {
@@ -877,7 +941,9 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
             }
             const int R = row0 + r;
             const size_t ri = (size_t) (q0 + R / G) * p.nh + kvh * G + R % G;
-            p.out[ri * HD + d] = __float2bfloat16_rn(l > 0.0f ? v / l : 0.0f);
+            float res = l > 0.0f ? v / l : 0.0f;
+            if (p.gate != nullptr) res *= gate_one(p, (size_t) (q0 + R / G), (kvh * G + R % G) * HD + d);
+            p.out[ri * HD + d] = __float2bfloat16_rn(res);
         }
         cluster.sync();                                      // nobody leaves while its shared memory is being read
         return;
@@ -916,8 +982,11 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
         const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
         __nv_bfloat16 * dst = p.out + row_idx * HD + mpart * (HD / 8);
 #pragma unroll
-        for (int c = 0; c < HD / 8; c += 2)
-            *reinterpret_cast<__nv_bfloat162 *>(dst + c) = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+        for (int c = 0; c < HD / 8; c += 2) {
+            float2 gt = make_float2(1.0f, 1.0f);
+            if (p.gate != nullptr) gt = gate_pair(p, (size_t) (q0 + mR / G), (kvh * G + mR % G) * HD + mpart * (HD / 8) + c);
+            *reinterpret_cast<__nv_bfloat162 *>(dst + c) = __floats2bfloat162_rn(acc[c] * inv * gt.x, acc[c + 1] * inv * gt.y);
+        }
     }
     if (tid == 0) *counter = 0;
 }
@@ -1123,6 +1192,13 @@ IIAN_API int iian_attention_mma_sink(
     int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
     float scale, int window, int n_split, int small_tiles, int * status, const float * sink, cudaStream_t stream);
 
+IIAN_API int iian_attention_mma_masked(
+    const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
+    int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, int chunk, int n_split, int small_tiles, int * status, const float * sink,
+    const float * pen1, const float * pen2, const void * gate, long long ld_gate, cudaStream_t stream);
+
 IIAN_API int iian_attention_mma(
     const void * q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
     int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
@@ -1139,8 +1215,29 @@ IIAN_API int iian_attention_mma_sink(
     int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
     int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
     float scale, int window, int n_split, int small_tiles, int * status, const float * sink, cudaStream_t stream) {
+    return iian_attention_mma_masked(q, (long long) nh * hd, k_cache, v_cache, out, part_o, part_lse, counters, cu_q, ctx_len,
+                                     block_table, max_blocks, N, S, max_q_len, nh, nkv, hd, page_size, num_pages, scale, window, 0,
+                                     n_split, small_tiles, status, sink, nullptr, nullptr, nullptr, 0, stream);
+}
+
+// The general entry.  q: rows of nh * hd with ld_q elements between them (a multiple of 8).  chunk > 0 (not together
+// with a window): key j is visible to position i iff j <= i and floor(i / chunk) == floor(j / chunk).  pen1, pen2:
+// f32 [nh] or both null: pen1[h] * ln(1 + pen2[h] * (i - j)) is taken off the scaled score (needs scale > 0).
+// gate: rows of nh * hd bf16 with ld_gate elements between them (even), or null: the output is multiplied by
+// sigmoid(gate) (not with split keys in the prefill form, whose merge is a kernel of its own).
+IIAN_API int iian_attention_mma_masked(
+    const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
+    int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, int chunk, int n_split, int small_tiles, int * status, const float * sink,
+    const float * pen1, const float * pen2, const void * gate, long long ld_gate, cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
     if (sink != nullptr && !(scale > 0.0f)) return IIAN_ERR_SHAPE;
+    if ((pen1 == nullptr) != (pen2 == nullptr) || (pen1 != nullptr && !(scale > 0.0f))) return IIAN_ERR_SHAPE;
+    if (chunk < 0 || (chunk > 0 && window > 0)) return IIAN_ERR_SHAPE;
+    if (ld_q < (long long) nh * hd || (ld_q & 7) || ((uintptr_t) q & 15)) return IIAN_ERR_ALIGN;
+    if (gate != nullptr && ((ld_gate & 1) || ((uintptr_t) gate & 3) || ld_gate < (long long) nh * hd)) return IIAN_ERR_ALIGN;
+    if (gate != nullptr && n_split > 1 && !small_tiles) return IIAN_ERR_SHAPE;
     if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
     if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
     const bool cluster = small_tiles == 2 && n_split > 1;   // decode form, parts merged inside a thread-block cluster
@@ -1159,6 +1256,11 @@ IIAN_API int iian_attention_mma_sink(
     p.status = ((uintptr_t) k_cache & 15) || ((uintptr_t) v_cache & 15) ? nullptr : status;
     p.sink = sink;
     p.sink_to_raw = sink != nullptr ? 1.0f / scale : 0.0f;
+    p.ld_q = ld_q;
+    p.chunk = chunk;
+    p.pen1 = pen1; p.pen2 = pen2;
+    p.pen_to_raw = pen1 != nullptr ? 1.0f / p.scale_log2 : 0.0f;
+    p.gate = (const __nv_bfloat16 *) gate; p.ld_gate = ld_gate;
     const int max_rows = max_q_len * (nh / nkv);
     int rc;
     if (cluster) rc = hd == 128 ? launch_decode<128, true>(p, S, max_rows, stream) : launch_decode<64, true>(p, S, max_rows, stream);

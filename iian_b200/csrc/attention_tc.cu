@@ -51,6 +51,16 @@ struct TcAttnParams {
     // a sink per head: a logit without key and value that joins the softmax's denominator once, not scaled
     const float * sink = nullptr;   // [nh] or null
     float sink_to_raw = 0.0f;       // 1 / scale: maxima are kept of raw scores, the scale enters in the exponent
+    long long ld_q = 0;             // elements between the rows of q (nh * 128 when q is contiguous)
+    // chunked mask: key j is visible to position i only if floor(i / chunk) == floor(j / chunk) (0: no chunks)
+    int chunk = 0;
+    // a penalty on distance, taken off the scaled score: pen1[h] * ln(1 + pen2[h] * (i - j)); null: none
+    const float * pen1 = nullptr;   // [nh]
+    const float * pen2 = nullptr;   // [nh]
+    float pen_to_raw = 0.0f;        // 1 / scale_log2: pen1 * log2(1 + pen2 d) in units of raw scores
+    // the output times sigmoid(gate): rows of nh * 128 with ld_gate elements between them; null: none
+    const __nv_bfloat16 * gate = nullptr;
+    long long ld_gate = 0;
 };
 
 __device__ __forceinline__ unsigned at_smem(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
@@ -189,7 +199,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     const int tok_min = row0 / G;
     const int k_hi_a = pos0 + min(rows_total - 1, row0 + AT_BM - 1) / G;
     const int k_hi = pos0 + min(rows_total - 1, row0 + AT_ROWS - 1) / G;
-    const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : 0;
+    const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1)
+                                  : p.chunk > 0 ? (pos0 + tok_min) - (pos0 + tok_min) % p.chunk : 0;
     const int tile_lo = k_lo / AT_BN, tile_hi = k_hi / AT_BN;
     const int n_tiles = tile_hi - tile_lo + 1;
     const int n_grp[2] = {k_hi_a / AT_BN - tile_lo + 1, has_b ? n_tiles : 0};
@@ -239,7 +250,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                 buf[u] = make_uint4(0u, 0u, 0u, 0u);
                 if (idx < AT_ROWS * 16 && R < rows_total) {
                     const int tok = R / G, head = kvh * G + R % G;
-                    buf[u] = *reinterpret_cast<const uint4 *>(p.q + ((size_t) (q0 + tok) * p.nh + head) * AT_HD + c * 8);
+                    buf[u] = *reinterpret_cast<const uint4 *>(p.q + (size_t) (q0 + tok) * p.ld_q + (size_t) head * AT_HD + c * 8);
                 }
             }
 #pragma unroll
@@ -370,6 +381,13 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             l_run = 1.0f;
         }
         const float sl = p.scale_log2;
+        const int row_lo = p.chunk > 0 ? row_pos - row_pos % p.chunk : 0;         // first key of the row's chunk
+        const bool two_sided = p.window > 0 || p.chunk > 0;
+        float pen_a = 0.0f, pen_b = 0.0f;
+        if (p.pen1 != nullptr && row_ok) {
+            pen_a = p.pen1[kvh * G + R % G] * p.pen_to_raw;
+            pen_b = p.pen2[kvh * G + R % G];
+        }
         bool failed = false;
         for (int i = 0; i < n_mine; i++) {
             const unsigned ph = (unsigned) i & 1u;
@@ -383,9 +401,15 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             at_wait_ld();
             // visible keys of this row in this tile: columns [lo, hi]; most tiles lie wholly below the diagonal
             const int hi = row_ok ? min(AT_BN - 1, row_pos - key0) : -1;
-            const int lo = p.window > 0 ? max(0, row_pos - p.window + 1 - key0) : 0;
+            const int lo = p.window > 0 ? max(0, row_pos - p.window + 1 - key0) : max(0, row_lo - key0);
+            if (p.pen1 != nullptr) {                // the distance penalty, in units of raw scores (masked keys are set below)
+                const float d0 = (float) (row_pos - key0);
+#pragma unroll
+                for (int j = 0; j < AT_BN; j++)
+                    v[j] = __float_as_uint(fmaf(-pen_a, __log2f(fmaf(pen_b, d0 - (float) j, 1.0f)), __uint_as_float(v[j])));
+            }
             if (!__all_sync(0xffffffffu, lo <= 0 && hi >= AT_BN - 1)) {
-                if (p.window > 0) {
+                if (two_sided) {
 #pragma unroll
                     for (int j = 0; j < AT_BN; j++)
                         if (j < lo || j > hi) v[j] = 0xff800000u;        // -inf
@@ -465,9 +489,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                 at_fence_after();
                 const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
                 __nv_bfloat16 * dst = nullptr;
+                const __nv_bfloat16 * gsrc = nullptr;
                 if (row_ok) {
                     const int tok = R / G, head = kvh * G + R % G;
                     dst = p.out + ((size_t) (q0 + tok) * p.nh + head) * AT_HD;
+                    if (p.gate != nullptr) gsrc = p.gate + (size_t) (q0 + tok) * p.ld_gate + (size_t) head * AT_HD;
                 }
                 unsigned o[AT_HD];                  // the whole row at once: one wait for four loads
 #pragma unroll
@@ -477,6 +503,16 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
 #pragma unroll
                     for (int q8 = 0; q8 < AT_HD / 8; q8++) {
                         uint4 pk;
+                        if (gsrc != nullptr) {          // times sigmoid(gate), eight columns at a time
+                            const uint4 gv = *reinterpret_cast<const uint4 *>(gsrc + 8 * q8);
+                            const unsigned gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const float2 gf = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&gw[e]));
+                                o[8 * q8 + 2 * e] = __float_as_uint(__uint_as_float(o[8 * q8 + 2 * e]) / (1.0f + __expf(-gf.x)));
+                                o[8 * q8 + 2 * e + 1] = __float_as_uint(__uint_as_float(o[8 * q8 + 2 * e + 1]) / (1.0f + __expf(-gf.y)));
+                            }
+                        }
                         __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(o[8 * q8 + 0]) * inv, __uint_as_float(o[8 * q8 + 1]) * inv);
                         __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(o[8 * q8 + 2]) * inv, __uint_as_float(o[8 * q8 + 3]) * inv);
                         __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(o[8 * q8 + 4]) * inv, __uint_as_float(o[8 * q8 + 5]) * inv);
@@ -540,6 +576,11 @@ IIAN_API int iian_attention_tc_sink(const void * q, const void * k_cache, const 
                                     const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
                                     int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
                                     float scale, int window, int * status, const float * sink, cudaStream_t stream);
+IIAN_API int iian_attention_tc_masked(const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out,
+                                      const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+                                      int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+                                      float scale, int window, int chunk, int * status, const float * sink, const float * pen1,
+                                      const float * pen2, const void * gate, long long ld_gate, cudaStream_t stream);
 
 IIAN_API int iian_attention_tc(const void * q, const void * k_cache, const void * v_cache, void * out,
                                const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
@@ -554,8 +595,27 @@ IIAN_API int iian_attention_tc_sink(const void * q, const void * k_cache, const 
                                     const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
                                     int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
                                     float scale, int window, int * status, const float * sink, cudaStream_t stream) {
+    return iian_attention_tc_masked(q, (long long) nh * hd, k_cache, v_cache, out, cu_q, ctx_len, block_table, max_blocks, N, S,
+                                    max_q_len, nh, nkv, hd, page_size, num_pages, scale, window, 0, status, sink, nullptr, nullptr,
+                                    nullptr, 0, stream);
+}
+
+// The general entry.  q: rows of nh * 128 with ld_q elements between them (a multiple of 8).  chunk > 0 (not together
+// with a window): key j is visible to position i iff j <= i and floor(i / chunk) == floor(j / chunk).  pen1, pen2: f32
+// [nh] or both null: pen1[h] * ln(1 + pen2[h] * (i - j)) is taken off the scaled score (needs scale > 0).  gate: rows of
+// nh * 128 bf16 with ld_gate elements between them (a multiple of 8, 16-byte aligned), or null: the output is multiplied
+// by sigmoid(gate).
+IIAN_API int iian_attention_tc_masked(const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out,
+                                      const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+                                      int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+                                      float scale, int window, int chunk, int * status, const float * sink, const float * pen1,
+                                      const float * pen2, const void * gate, long long ld_gate, cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
     if (sink != nullptr && !(scale > 0.0f)) return IIAN_ERR_SHAPE;
+    if ((pen1 == nullptr) != (pen2 == nullptr) || (pen1 != nullptr && !(scale > 0.0f))) return IIAN_ERR_SHAPE;
+    if (chunk < 0 || (chunk > 0 && window > 0)) return IIAN_ERR_SHAPE;
+    if (ld_q < (long long) nh * hd || (ld_q & 7)) return IIAN_ERR_ALIGN;
+    if (gate != nullptr && ((ld_gate & 7) || ((uintptr_t) gate & 15) || ld_gate < (long long) nh * hd)) return IIAN_ERR_ALIGN;
     if (hd != AT_HD || nkv <= 0 || nh % nkv != 0) return IIAN_ERR_SHAPE;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return IIAN_ERR_SHAPE;
     if (status == nullptr) return IIAN_ERR_SHAPE;
@@ -573,6 +633,11 @@ IIAN_API int iian_attention_tc_sink(const void * q, const void * k_cache, const 
     p.status = status;
     p.sink = sink;
     p.sink_to_raw = sink != nullptr ? 1.0f / scale : 0.0f;
+    p.ld_q = ld_q;
+    p.chunk = chunk;
+    p.pen1 = pen1; p.pen2 = pen2;
+    p.pen_to_raw = pen1 != nullptr ? 1.0f / p.scale_log2 : 0.0f;
+    p.gate = (const __nv_bfloat16 *) gate; p.ld_gate = ld_gate;
     const size_t smem = (size_t) 6 * AT_TILE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {

@@ -12,11 +12,12 @@
 // registers), and both dot products of a token are taken from the decayed column in ONE pass and reduced together.
 //
 // Kernels:
-//   delta_prep   per token: convolution + silu over the channels q | k | v (inputs of earlier tokens come from the rows
-//                before it in the step, or from the state's tail), unit length of q and k per head, q . k, sigmoid of the
-//                write strength, the decay exp(-exp(A) softplus(z + bias)).  Everything it leaves is float32.
-//   delta_scan   the recurrence over a step's tokens of every sequence, chunks of tokens through shared memory; the CTA
-//                of a sequence's first head and column block also moves the convolution's tail on.
+//   delta_prep   per token and head: convolution + silu over the channels q | k | v (inputs of earlier tokens come from
+//                the rows before it in the step, or from the state's tail), unit length of q and k per head, q . k, sigmoid
+//                of the write strength, the decay exp(-exp(A) softplus(z + bias)).  Everything it leaves is float32.
+//   delta_scan   the recurrence over a step's tokens of every sequence; the tokens' vectors come through two stages of
+//                shared memory filled by cp.async a chunk ahead; the CTA of a sequence's first head and column block also
+//                moves the convolution's tail on.
 // State of a slot (float32): S as [heads, vdim, dim] (a column is contiguous), then the tail [taps - 1, channels].
 #include "common.cuh"
 
@@ -29,96 +30,133 @@ constexpr int kMaxTaps = 8;
 
 // proj rows: [.. q (G * D) | k (G * D) | v (H * V) .. | b (H) ..] at col_off / b_off, row stride ld, activation type A.
 // z: float32 [N, H * D] (the decay's pre-activation without its bias).  taps: float32 [C, n_taps], C = 2 G D + H V.
+// Grid (N, G + H): CTA (t, u) with u < G prepares query/key head u of token t (convolution, silu, unit length, q . k);
+// with u >= G the values of head u - G (convolution, silu), that head's decays and its write strength -- so that a step of
+// a few single tokens still spreads over the GPU.
+constexpr int kPrepThreads = 128;
+constexpr int kPrepMaxDim = 512;
+
 template <typename A>
-__global__ void delta_prep_kernel(const A * __restrict__ proj, long long ld, int col_off, int b_off,
-                                  const float * __restrict__ z, const float * __restrict__ taps, int n_taps,
-                                  const float * __restrict__ a_log, const float * __restrict__ dt_bias,
-                                  const float * __restrict__ state, long long state_stride, long long tail_off,
-                                  const int * __restrict__ seq_of_token, const int * __restrict__ cu_q,
-                                  const int * __restrict__ state_slots,
-                                  float * __restrict__ qn, float * __restrict__ kn, float * __restrict__ vv,
-                                  float * __restrict__ beta, float * __restrict__ decay, float * __restrict__ qk,
-                                  int H, int G, int D, int V, float q_scale) {
+__device__ __forceinline__ float delta_conv(const A * __restrict__ proj, long long ld, int col, long long t, int first,
+                                            const float * __restrict__ tail, int C, int c, const float * __restrict__ taps,
+                                            int n_taps) {
+    const int back = n_taps - 1;
+    float x[kMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; j++) {
+        x[j] = 0.0f;
+        if (j < n_taps) {
+            const long long r = t - back + j;                          // the row that tap j multiplies
+            if (r >= first) x[j] = to_f32(proj[(size_t) r * ld + col]);
+            else {
+                const int idx = (int) (r - first) + back;              // place in the tail: rows first - back .. first - 1
+                if (tail != nullptr && idx >= 0) x[j] = tail[(size_t) idx * C + c];
+            }
+        }
+    }
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; j++)
+        if (j < n_taps) acc = fmaf(taps[(size_t) c * n_taps + j], x[j], acc);
+    return acc;
+}
+
+template <typename A>
+__global__ void __launch_bounds__(kPrepThreads)
+delta_prep_kernel(const A * __restrict__ proj, long long ld, int col_off, int b_off,
+                  const float * __restrict__ z, const float * __restrict__ taps, int n_taps,
+                  const float * __restrict__ a_log, const float * __restrict__ dt_bias,
+                  const float * __restrict__ state, long long state_stride, long long tail_off,
+                  const int * __restrict__ seq_of_token, const int * __restrict__ cu_q,
+                  const int * __restrict__ state_slots,
+                  float * __restrict__ qn, float * __restrict__ kn, float * __restrict__ vv,
+                  float * __restrict__ beta, float * __restrict__ decay, float * __restrict__ qk,
+                  int H, int G, int D, int V, float q_scale) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float act[];            // [2 G D] the activated q | k channels of this token
-    __shared__ float red[32];
+    __shared__ float act_q[kPrepMaxDim], act_k[kPrepMaxDim];
+    __shared__ float red[3][kPrepThreads / 32];
     const size_t t = blockIdx.x;
+    const int u = blockIdx.y;
     const int s = seq_of_token[t];
     const int GD = G * D, HV = H * V, C = 2 * GD + HV;
     if (s < 0) return;                         // padding token: the scan writes zeros for it
     const int slot = state_slots[s];
     const int first = cu_q[s];                 // the step's first row of this sequence
     const float * tail = slot >= 0 ? state + (size_t) slot * state_stride + tail_off : nullptr;
-    const int back = n_taps - 1;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float acc = 0.0f;
-        for (int j = 0; j < n_taps; j++) {
-            const long long r = (long long) t - back + j;              // the row that tap j multiplies
-            float x;
-            if (r >= first) x = to_f32(proj[(size_t) r * ld + col_off + c]);
-            else {
-                const int idx = (int) (r - first) + back;              // place in the tail: rows first - back .. first - 1
-                x = (tail != nullptr && idx >= 0) ? tail[(size_t) idx * C + c] : 0.0f;
-            }
-            acc = fmaf(taps[(size_t) c * n_taps + j], x, acc);
-        }
-        const float a = silu_f32(acc);
-        if (c < 2 * GD) act[c] = a;
-        else vv[t * HV + (c - 2 * GD)] = a;
-    }
-    __syncthreads();
-    // unit length per head of q and of k, and q . k: one warp per head
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int g = warp; g < G; g += warps) {
-        const float * qa = act + g * D;
-        const float * ka = act + GD + g * D;
+    if (u < G) {
         float sq = 0.0f, sk = 0.0f, dot = 0.0f;
-        for (int d = lane; d < D; d += 32) {
-            sq = fmaf(qa[d], qa[d], sq);
-            sk = fmaf(ka[d], ka[d], sk);
-            dot = fmaf(qa[d], ka[d], dot);
+        for (int d = threadIdx.x; d < D; d += kPrepThreads) {
+            const int cq = u * D + d, ck = GD + u * D + d;
+            const float a = silu_f32(delta_conv(proj, ld, col_off + cq, (long long) t, first, tail, C, cq, taps, n_taps));
+            const float b = silu_f32(delta_conv(proj, ld, col_off + ck, (long long) t, first, tail, C, ck, taps, n_taps));
+            act_q[d] = a;
+            act_k[d] = b;
+            sq = fmaf(a, a, sq);
+            sk = fmaf(b, b, sk);
+            dot = fmaf(a, b, dot);
         }
         sq = warp_sum(sq);
         sk = warp_sum(sk);
         dot = warp_sum(dot);
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; red[2][warp] = dot; }
+        __syncthreads();
+        sq = sk = dot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kPrepThreads / 32; w++) { sq += red[0][w]; sk += red[1][w]; dot += red[2][w]; }
         const float iq = q_scale / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
-        for (int d = lane; d < D; d += 32) {
-            qn[t * GD + g * D + d] = qa[d] * iq;
-            kn[t * GD + g * D + d] = ka[d] * ik;
+        for (int d = threadIdx.x; d < D; d += kPrepThreads) {
+            qn[t * GD + u * D + d] = act_q[d] * iq;
+            kn[t * GD + u * D + d] = act_k[d] * ik;
         }
-        if (lane == 0) qk[t * G + g] = dot * iq * ik;
+        if (threadIdx.x == 0) qk[t * G + u] = dot * iq * ik;
+        return;
     }
-    for (int h = threadIdx.x; h < H; h += blockDim.x)
-        beta[t * H + h] = 1.0f / (1.0f + expf(-to_f32(proj[t * ld + b_off + h])));
-    for (int e = threadIdx.x; e < H * D; e += blockDim.x) {
-        const int h = e / D;
-        decay[t * (size_t) (H * D) + e] = expf(-expf(a_log[h]) * softplus_f32(z[t * (size_t) (H * D) + e] + dt_bias[e]));
+    const int h = u - G;
+    for (int j = threadIdx.x; j < V; j += kPrepThreads) {
+        const int c = 2 * GD + h * V + j;
+        vv[t * HV + h * V + j] = silu_f32(delta_conv(proj, ld, col_off + c, (long long) t, first, tail, C, c, taps, n_taps));
     }
-    (void) red;
+    const float rate = expf(a_log[h]);
+    for (int d = threadIdx.x; d < D; d += kPrepThreads) {
+        const size_t e = (size_t) h * D + d;
+        decay[t * (size_t) (H * D) + e] = expf(-rate * softplus_f32(z[t * (size_t) (H * D) + e] + dt_bias[e]));
+    }
+    if (threadIdx.x == 0) beta[t * H + h] = 1.0f / (1.0f + expf(-to_f32(proj[t * ld + b_off + h])));
 }
 
 constexpr int kCols = 16;        // columns of S a CTA owns
 constexpr int kLanes = 8;        // lanes that share a column
-constexpr int kChunk = 16;       // tokens that wait in shared memory at a time
 
-// E: entries of a column a lane holds (entry d = lane + kLanes * i)
-template <int E, typename A>
+__device__ __forceinline__ void dr_cp4(float * dst, const float * src, bool valid) {
+    const unsigned d = (unsigned) __cvta_generic_to_shared(dst);
+    const int n = valid ? 4 : 0;                             // src-size 0: the word is zero-filled, nothing is read
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void dr_cp16(float * dst, const float * src) {
+    const unsigned d = (unsigned) __cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void dr_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+// E: entries of a column a lane holds (entry d = lane + kLanes * i).  VEC: rows of q, k and the decays are copied 16 bytes
+// at a time (D a multiple of 4 and the buffers 16-byte aligned), else word by word.  The tokens of a sequence pass through
+// two stages of shared memory, `chunk` tokens each: while one is worked through, cp.async fills the other.
+template <int E, bool VEC, typename A>
 __global__ void __launch_bounds__(kCols * kLanes)
 delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, const float * __restrict__ vv,
                   const float * __restrict__ beta, const float * __restrict__ decay, const float * __restrict__ qk,
                   float * __restrict__ state, long long state_stride, long long tail_off,
                   const A * __restrict__ proj, long long ld, int col_off, int n_taps,
                   const int * __restrict__ cu_q, const int * __restrict__ state_slots, float * __restrict__ out,
-                  int H, int G, int D, int V) {
+                  int H, int G, int D, int V, int chunk) {
     pdl_wait();
     pdl_launch_dependents();
-    extern __shared__ float sm[];
-    float * s_q = sm;                          // [kChunk][D]
-    float * s_k = s_q + kChunk * D;            // [kChunk][D]
-    float * s_g = s_k + kChunk * D;            // [kChunk][D]
-    float * s_v = s_g + kChunk * D;            // [kChunk][kCols]
-    float * s_b = s_v + kChunk * kCols;        // [kChunk] beta, [kChunk] q . k
+    extern __shared__ __align__(16) float sm[];
+    const int Dp = (D + 3) & ~3;                             // rows start on 16-byte boundaries
+    const int stage_floats = chunk * (3 * Dp + kCols + 4);   // q | k | decay | v | beta, q . k (padded to 4 per token)
     const int cb = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
     const int g = h / (H / G);
     const int col = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
@@ -132,6 +170,45 @@ delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, 
         return;
     }
     float * st = state + (size_t) slot * state_stride;
+
+    auto fill = [&](int c0, int stage) {       // tokens c0 .. of the step into a stage
+        const int nt = min(chunk, t1 - c0);
+        float * s_q = sm + (size_t) stage * stage_floats;
+        float * s_k = s_q + chunk * Dp;
+        float * s_g = s_k + chunk * Dp;
+        float * s_v = s_g + chunk * Dp;
+        float * s_b = s_v + chunk * kCols;
+        if (VEC) {
+            const int per = D >> 2;
+            for (int e = threadIdx.x; e < nt * per; e += blockDim.x) {
+                const int tt = e / per, d = (e - tt * per) << 2;
+                const size_t t = c0 + tt;
+                dr_cp16(s_q + tt * Dp + d, qn + t * GD + g * D + d);
+                dr_cp16(s_k + tt * Dp + d, kn + t * GD + g * D + d);
+                dr_cp16(s_g + tt * Dp + d, decay + t * HD + h * D + d);
+            }
+        } else {
+            for (int e = threadIdx.x; e < nt * D; e += blockDim.x) {
+                const int tt = e / D, d = e - tt * D;
+                const size_t t = c0 + tt;
+                dr_cp4(s_q + tt * Dp + d, qn + t * GD + g * D + d, true);
+                dr_cp4(s_k + tt * Dp + d, kn + t * GD + g * D + d, true);
+                dr_cp4(s_g + tt * Dp + d, decay + t * HD + h * D + d, true);
+            }
+        }
+        for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
+            const int tt = e / kCols, c = e - tt * kCols;
+            const int jj = cb * kCols + c;
+            dr_cp4(s_v + e, vv + (size_t) (c0 + tt) * HV + h * V + (jj < V ? jj : 0), jj < V);
+        }
+        for (int e = threadIdx.x; e < nt; e += blockDim.x) {
+            dr_cp4(s_b + 2 * e, beta + (size_t) (c0 + e) * H + h, true);
+            dr_cp4(s_b + 2 * e + 1, qk + (size_t) (c0 + e) * G + g, true);
+        }
+    };
+    if (t0 < t1) fill(t0, 0);
+    dr_commit();
+
     // the convolution's tail moves on: the last taps - 1 inputs of the sequence so far (one CTA per sequence does it)
     if (cb == 0 && h == 0 && n_taps > 1) {
         const int C = 2 * GD + HV, back = n_taps - 1, L = t1 - t0;
@@ -159,53 +236,56 @@ delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, 
         const int d = lane + kLanes * i;
         S[i] = (j < V && d < D) ? scol[d] : 0.0f;
     }
-    for (int c0 = t0; c0 < t1; c0 += kChunk) {
-        const int nt = min(kChunk, t1 - c0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < nt * D; e += blockDim.x) {
-            const int tt = e / D, d = e - tt * D;
-            const size_t t = c0 + tt;
-            s_q[tt * D + d] = qn[t * GD + g * D + d];
-            s_k[tt * D + d] = kn[t * GD + g * D + d];
-            s_g[tt * D + d] = decay[t * HD + h * D + d];
-        }
-        for (int e = threadIdx.x; e < nt * kCols; e += blockDim.x) {
-            const int tt = e / kCols, c = e - tt * kCols;
-            const int jj = cb * kCols + c;
-            s_v[e] = jj < V ? vv[(size_t) (c0 + tt) * HV + h * V + jj] : 0.0f;
-        }
-        for (int e = threadIdx.x; e < nt; e += blockDim.x) {
-            s_b[e] = beta[(size_t) (c0 + e) * H + h];
-            s_b[kChunk + e] = qk[(size_t) (c0 + e) * G + g];
+    int stage = 0;
+    for (int c0 = t0; c0 < t1; c0 += chunk, stage ^= 1) {
+        const int nt = min(chunk, t1 - c0);
+        if (c0 + chunk < t1) {
+            fill(c0 + chunk, stage ^ 1);       // (the stage was read two chunks ago; the barrier below closed that)
+            dr_commit();
+            dr_wait<1>();
+        } else {
+            dr_wait<0>();
         }
         __syncthreads();
+        const float * s_q = sm + (size_t) stage * stage_floats;
+        const float * s_k = s_q + chunk * Dp;
+        const float * s_g = s_k + chunk * Dp;
+        const float * s_v = s_g + chunk * Dp;
+        const float * s_b = s_v + chunk * kCols;
         for (int tt = 0; tt < nt; tt++) {
-            const float * kq = s_k + tt * D;
-            const float * qq = s_q + tt * D;
-            const float * gg = s_g + tt * D;
-            float a = 0.0f, b = 0.0f;
+            const float * kq = s_k + tt * Dp;
+            const float * qq = s_q + tt * Dp;
+            const float * gg = s_g + tt * Dp;
+            float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < E; i++) {
+            for (int i = 0; i < E; i += 2) {
                 const int d = lane + kLanes * i;
                 if (d < D) {
                     S[i] *= gg[d];
-                    a = fmaf(kq[d], S[i], a);
-                    b = fmaf(qq[d], S[i], b);
+                    a0 = fmaf(kq[d], S[i], a0);
+                    b0 = fmaf(qq[d], S[i], b0);
+                }
+                if (d + kLanes < D) {
+                    S[i + 1] *= gg[d + kLanes];
+                    a1 = fmaf(kq[d + kLanes], S[i + 1], a1);
+                    b1 = fmaf(qq[d + kLanes], S[i + 1], b1);
                 }
             }
+            float a = a0 + a1, b = b0 + b1;
 #pragma unroll
             for (int o = kLanes / 2; o > 0; o >>= 1) {
                 a += __shfl_xor_sync(0xffffffffu, a, o);
                 b += __shfl_xor_sync(0xffffffffu, b, o);
             }
-            const float u = s_b[tt] * (s_v[tt * kCols + col] - a);
+            const float u = s_b[2 * tt] * (s_v[tt * kCols + col] - a);
 #pragma unroll
             for (int i = 0; i < E; i++) {
                 const int d = lane + kLanes * i;
                 if (d < D) S[i] = fmaf(kq[d], u, S[i]);
             }
-            if (lane == 0 && j < V) out[(size_t) (c0 + tt) * HV + h * V + j] = fmaf(s_b[kChunk + tt], u, b);
+            if (lane == 0 && j < V) out[(size_t) (c0 + tt) * HV + h * V + j] = fmaf(s_b[2 * tt + 1], u, b);
         }
+        __syncthreads();                       // everyone is done with this stage before it is filled again
     }
     if (j < V) {
 #pragma unroll
@@ -232,22 +312,19 @@ IIAN_API int iian_delta_prep(const void * proj, long long ld, int col_off, int b
                              int D, int V, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0 || n_taps < 1 || n_taps > kMaxTaps) return IIAN_ERR_SHAPE;
-    const size_t smem = (size_t) 2 * G * D * sizeof(float);
-    if (smem > 200 * 1024) return IIAN_ERR_LIMIT;
+    if (D > kPrepMaxDim) return IIAN_ERR_LIMIT;
+    if (G + H > 65535) return IIAN_ERR_LIMIT;
     const long long tail_off = (long long) H * V * D;
     const float q_scale = 1.0f / sqrtf((float) D);
-    if (act_dtype == IIAN_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
-        return iian_launch(delta_prep_kernel<float>, dim3(N), dim3(256), smem, stream, (const float *) proj, ld, col_off, b_off, z,
+    const dim3 grid(N, G + H);
+    if (act_dtype == IIAN_F32)
+        return iian_launch(delta_prep_kernel<float>, grid, dim3(kPrepThreads), 0, stream, (const float *) proj, ld, col_off, b_off, z,
                            taps, n_taps, a_log, dt_bias, state, state_stride, tail_off, seq_of_token, cu_q, state_slots, qn, kn,
                            vv, beta, decay, qk, H, G, D, V, q_scale);
-    }
-    if (act_dtype == IIAN_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
-        return iian_launch(delta_prep_kernel<__nv_bfloat16>, dim3(N), dim3(256), smem, stream, (const __nv_bfloat16 *) proj, ld,
+    if (act_dtype == IIAN_BF16)
+        return iian_launch(delta_prep_kernel<__nv_bfloat16>, grid, dim3(kPrepThreads), 0, stream, (const __nv_bfloat16 *) proj, ld,
                            col_off, b_off, z, taps, n_taps, a_log, dt_bias, state, state_stride, tail_off, seq_of_token, cu_q,
                            state_slots, qn, kn, vv, beta, decay, qk, H, G, D, V, q_scale);
-    }
     return IIAN_ERR_DTYPE;
 }
 
@@ -256,12 +333,20 @@ static int launch_scan(const float * qn, const float * kn, const float * vv, con
                        const float * qk, float * state, long long state_stride, const A * proj, long long ld, int col_off,
                        int n_taps, const int * cu_q, const int * state_slots, float * out, int S, int H, int G, int D, int V,
                        cudaStream_t stream) {
-    const size_t smem = ((size_t) kChunk * (3 * D + kCols) + 2 * kChunk) * sizeof(float);
+    const int Dp = (D + 3) & ~3;
+    const int chunk = D <= 256 ? 16 : 8;       // tokens per stage of shared memory
+    const size_t smem = (size_t) 2 * chunk * (3 * Dp + kCols + 4) * sizeof(float);
     if (smem > 200 * 1024) return IIAN_ERR_LIMIT;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<E, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+    const bool vec = D % 4 == 0 && (((uintptr_t) qn | (uintptr_t) kn | (uintptr_t) decay) & 15) == 0;
     const dim3 grid((V + kCols - 1) / kCols, H, S);
-    return iian_launch(delta_scan_kernel<E, A>, grid, dim3(kCols * kLanes), smem, stream, qn, kn, vv, beta, decay, qk, state,
-                       state_stride, (long long) H * V * D, proj, ld, col_off, n_taps, cu_q, state_slots, out, H, G, D, V);
+    if (vec) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<E, true, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        return iian_launch(delta_scan_kernel<E, true, A>, grid, dim3(kCols * kLanes), smem, stream, qn, kn, vv, beta, decay, qk, state,
+                           state_stride, (long long) H * V * D, proj, ld, col_off, n_taps, cu_q, state_slots, out, H, G, D, V, chunk);
+    }
+    if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<E, false, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+    return iian_launch(delta_scan_kernel<E, false, A>, grid, dim3(kCols * kLanes), smem, stream, qn, kn, vv, beta, decay, qk, state,
+                       state_stride, (long long) H * V * D, proj, ld, col_off, n_taps, cu_q, state_slots, out, H, G, D, V, chunk);
 }
 
 template <typename A>

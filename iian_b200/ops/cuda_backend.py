@@ -1436,16 +1436,24 @@ class CudaKernels:
     def chunked_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, meta, *,
                           num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float, chunk: Optional[int],
                           window: Optional[int], r1: Optional[torch.Tensor], r2: Optional[torch.Tensor],
-                          gate: Optional[torch.Tensor]) -> None:
+                          gate: Optional[torch.Tensor], n_split: Optional[int] = None) -> None:
         """``q`` rows of ``heads * k_dim`` (may be a column slice) -> ``out`` [N, heads * v_dim]: softmax of
         ``q . k * scale - r1 ln(1 + r2 (i - j))`` over the keys ``j <= i`` of position ``i``'s chunk (or window), weighted sum
-        of the cached values, times ``sigmoid(gate)`` if given (rows of ``heads * v_dim``, may be a column slice)."""
+        of the cached values, times ``sigmoid(gate)`` if given (rows of ``heads * v_dim``, may be a column slice).
+        In bfloat16 with keys and values of 64 or 128 entries and a positive scale the tensor-core kernels of
+        ``csrc/attention_mma.cu`` serve it (mask, penalty and gate inside them); otherwise the general kernel of
+        ``csrc/chunked_attention.cu``.  ``n_split``: the key parts of the decode form that a captured graph fixed."""
         n = q.shape[0]
         qp, ld_q = self._rows(q, "queries")
         gp, ld_g = self._rows(gate, "gate")
         if q.shape[1] != num_heads * k_dim or out.shape != (n, num_heads * v_dim) or out.dtype != q.dtype or k_cache.dtype != q.dtype \
                 or (gate is not None and (gate.shape != out.shape or gate.dtype != q.dtype)) or (r1 is None) != (r2 is None):
             raise KernelError(f"chunked_attention: q {tuple(q.shape)}, out {tuple(out.shape)} do not fit")
+        if self.chunked_attention_mma_ok(q.dtype, num_heads, num_kv_heads, k_dim, v_dim, scale) and ld_q % 8 == 0 \
+                and qp % 16 == 0 and (gate is None or (ld_g % 2 == 0 and gp % 4 == 0)):
+            self._chunked_attention_mma(qp, ld_q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, k_dim, scale, chunk, window,
+                                        r1, r2, gp, ld_g, n, n_split)
+            return
         bt = meta.block_table
         fn = _fn("chunked_attention", "iian_chunked_attention",
                  [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
@@ -1455,6 +1463,67 @@ class CudaKernels:
                   _cuda(bt, "block table", torch.int32), bt.shape[1], _cuda(meta.ctx_len, "ctx_len", torch.int32), _code(q, "queries"),
                   n, num_heads, num_kv_heads, k_dim, v_dim, k_cache.shape[2], k_cache.shape[0], scale, chunk or 0, window or 0,
                   _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g, _stream()), "chunked_attention")
+
+    CHUNKED_ATTENTION_MMA = os.environ.get("IIAN_CHUNKED_ATTENTION_MMA", "1") not in ("0", "false", "off")
+
+    def chunked_attention_mma_ok(self, dtype, num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float) -> bool:
+        return (self.CHUNKED_ATTENTION_MMA and dtype == torch.bfloat16 and k_dim == v_dim and k_dim in (64, 128) and scale > 0
+                and num_kv_heads > 0 and num_heads % num_kv_heads == 0)
+
+    def chunked_attention_plan(self, num_seqs: int, num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float,
+                               max_ctx: int, chunk: Optional[int], window: Optional[int], dtype: torch.dtype):
+        """The number of key parts of the decode form is part of a captured graph (grid and cluster sizes)."""
+        if not self.chunked_attention_mma_ok(dtype, num_heads, num_kv_heads, k_dim, v_dim, scale):
+            return None
+        return {"n_split": self.attention_splits(num_seqs, num_kv_heads, min(max_ctx, chunk or window or max_ctx))}
+
+    def _chunked_attention_mma(self, qp, ld_q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, chunk, window, r1, r2, gp, ld_g,
+                               n, n_split) -> None:
+        if k_cache.shape[1] != nkv or k_cache.shape[3] != hd or v_cache.shape != k_cache.shape:
+            raise KernelError("chunked_attention: cache shapes do not match the head counts")
+        bt = meta.block_table
+        if self.ATTENTION_TC and hd == 128 and k_cache.shape[2] in (8, 16, 32, 64, 128) and ld_q % 8 == 0 \
+                and meta.max_q_len * (nh // nkv) >= self.TC_ATTENTION_MIN_ROWS and gp % 16 == 0 and ld_g % 8 == 0 \
+                and out.data_ptr() % 16 == 0:
+            # portions of prompts with heads of 128: tcgen05 (csrc/attention_tc.cu)
+            status = self.tcgen05_status_buffer(out.device)
+            CudaKernels._tc_used = True
+            fn = _fn("attention_tc", "iian_attention_tc_masked",
+                     [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_longlong, c_void_p])
+            _check(fn(qp, ld_q, _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"), _cuda(out, "attention out"),
+                      _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                      _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, nh, nkv, hd,
+                      k_cache.shape[2], k_cache.shape[0], scale, window or 0, chunk or 0, status.data_ptr(), None,
+                      _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g, _stream()), "chunked attention (tcgen05)")
+            return
+        if self._stages_set != self.DECODE_STAGES:
+            self.set_decode_stages(self.DECODE_STAGES)
+        small = meta.max_q_len * (nh // nkv) <= 16
+        if not small:
+            n_split = 1
+        elif n_split is None:
+            n_split = self.attention_splits(meta.num_seqs, nkv, min(meta.max_ctx, chunk or window or meta.max_ctx))
+        cluster = bool(self.CLUSTER_MERGE and small and n_split in (2, 4, 8, 16))
+        part_o = part_lse = counters = 0
+        if n_split > 1 and not cluster:
+            rows = n * nh
+            scratch = self.attention_scratch(out.device, rows * n_split * (hd + 1))
+            part_o = scratch.data_ptr()
+            part_lse = part_o + rows * n_split * hd * 4
+            row_tiles = -(-meta.max_q_len * (nh // nkv) // 16)
+            counters = self.attention_counters(out.device, meta.num_seqs * nkv * row_tiles).data_ptr()
+        fn = _fn("attention_mma", "iian_attention_mma_masked",
+                 [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p,
+                  c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p])
+        _check(fn(qp, ld_q, _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"), _cuda(out, "attention out"),
+                  part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
+                  _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, nh, nkv, hd,
+                  k_cache.shape[2], k_cache.shape[0], scale, window or 0, chunk or 0, n_split,
+                  (2 if cluster else 1) if small else 0, self._decode_status(out.device) if small else None, None,
+                  _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g, _stream()), "chunked attention (mma)")
 
     # ---- the delta rule with a decay per key channel (csrc/delta_rule.cu) ---------------------------------------------------
     @staticmethod

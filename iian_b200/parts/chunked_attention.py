@@ -89,7 +89,15 @@ class ChunkedAttention(Mixer):
         return KVNeed(self.nkv, self.hd, keep, self.vd if self.vd != self.hd else None)
 
     def kernel_libraries(self):
-        return ("chunked_attention", "gemm_simt")
+        fast = self.dtype == torch.bfloat16 and self.hd == self.vd and self.hd in (64, 128) and self.scale > 0
+        return ("chunked_attention", "gemm_simt") + (("attention_mma",) if fast else ()) + (("attention_tc",) if fast and self.hd == 128 else ())
+
+    def graph_plan(self, num_seqs: int, max_ctx: int):
+        k = ops.kernels()
+        if not hasattr(k, "chunked_attention_plan"):
+            return None
+        return k.chunked_attention_plan(num_seqs, self.nh, self.nkv, self.hd, self.vd, self.scale, max_ctx, self.chunk, self.window,
+                                        self.dtype)
 
     def forward(self, x, ctx, cache, writes_cache: bool):
         if writes_cache and not self.owns_kv:
@@ -106,9 +114,10 @@ class ChunkedAttention(Mixer):
                               v_dim=self.vd, eps=self.eps, norm_values=self.value_norm)
         gate = proj[:, self.q_size: front] if self.has_gate else None
         attn = ctx.buf("attn", (n, self.o_size), self.dtype)
+        plan = ctx.graph_plan(self)
         k.chunked_attention(proj[:, : self.q_size], cache.k, cache.v, attn, meta, num_heads=self.nh, num_kv_heads=self.nkv,
                             k_dim=self.hd, v_dim=self.vd, scale=self.scale, chunk=self.chunk, window=self.window, r1=self.r1,
-                            r2=self.r2, gate=gate)
+                            r2=self.r2, gate=gate, **({"n_split": plan["n_split"]} if plan else {}))
         out = ctx.buf("mixer_out", (n, self.hidden), self.dtype)
         k.linear(attn, self.w_o, out)
         return out

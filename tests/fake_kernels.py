@@ -403,7 +403,7 @@ class FakeKernels:
                 v_cache[c // ps, :, c % ps, :] = vv[t].to(v_cache.dtype)
 
     def chunked_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, k_dim, v_dim, scale, chunk, window,
-                          r1, r2, gate):
+                          r1, r2, gate, n_split=None):
         n = q.shape[0]
         ps = k_cache.shape[2]
         rep = num_heads // num_kv_heads
