@@ -16,8 +16,8 @@
 //                the rows before it in the step, or from the state's tail), unit length of q and k per head, q . k, sigmoid
 //                of the write strength, the decay exp(-exp(A) softplus(z + bias)).  Everything it leaves is float32.
 //   delta_scan   the recurrence over a step's tokens of every sequence; the tokens' vectors come through two stages of
-//                shared memory filled by cp.async a chunk ahead; the CTA of a sequence's first head and column block also
-//                moves the convolution's tail on.
+//                shared memory filled by cp.async a chunk ahead; the CTAs of a sequence also move the convolution's tail
+//                on, a share of the channels each.
 // State of a slot (float32): S as [heads, vdim, dim] (a column is contiguous), then the tail [taps - 1, channels].
 #include "common.cuh"
 
@@ -141,9 +141,10 @@ __device__ __forceinline__ void dr_cp16(float * dst, const float * src) {
 __device__ __forceinline__ void dr_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N> __device__ __forceinline__ void dr_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
 
-// E: entries of a column a lane holds (entry d = lane + kLanes * i).  VEC: rows of q, k and the decays are copied 16 bytes
-// at a time (D a multiple of 4 and the buffers 16-byte aligned), else word by word.  The tokens of a sequence pass through
-// two stages of shared memory, `chunk` tokens each: while one is worked through, cp.async fills the other.
+// E: entries of a column a lane holds.  VEC (D a multiple of 4, the buffers 16-byte aligned): a lane holds groups of four
+// neighbouring entries, d = 4 * lane + 32 * (i / 4) + i % 4, so that the state and the rows of q, k and the decays move
+// 16 bytes at a time (E a multiple of 4); else entry d = lane + kLanes * i, word by word.  The tokens of a sequence pass
+// through two stages of shared memory, `chunk` tokens each: while one is worked through, cp.async fills the other.
 template <int E, bool VEC, typename A>
 __global__ void __launch_bounds__(kCols * kLanes)
 delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, const float * __restrict__ vv,
@@ -209,11 +210,12 @@ delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, 
     if (t0 < t1) fill(t0, 0);
     dr_commit();
 
-    // the convolution's tail moves on: the last taps - 1 inputs of the sequence so far (one CTA per sequence does it)
-    if (cb == 0 && h == 0 && n_taps > 1) {
+    // the convolution's tail moves on: the last taps - 1 inputs of the sequence so far (the sequence's CTAs share the channels)
+    if (n_taps > 1) {
         const int C = 2 * GD + HV, back = n_taps - 1, L = t1 - t0;
         float * tail = st + tail_off;
-        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        const int part = h * gridDim.x + cb, parts = gridDim.x * gridDim.y;
+        for (int c = part * blockDim.x + threadIdx.x; c < C; c += parts * blockDim.x) {
             float keep[kMaxTaps];
 #pragma unroll
             for (int i = 0; i < kMaxTaps - 1; i++) {
@@ -231,10 +233,21 @@ delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, 
     }
     float S[E];
     float * scol = st + ((size_t) h * V + (j < V ? j : 0)) * D;
+    static_assert(!VEC || E % 4 == 0, "groups of four entries");
+    if (VEC) {
 #pragma unroll
-    for (int i = 0; i < E; i++) {
-        const int d = lane + kLanes * i;
-        S[i] = (j < V && d < D) ? scol[d] : 0.0f;
+        for (int i = 0; i < E; i += 4) {
+            const int d = 4 * lane + 4 * kLanes * (i >> 2);
+            float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (j < V && d < D) x = *reinterpret_cast<const float4 *>(scol + d);
+            S[i] = x.x; S[i + 1] = x.y; S[i + 2] = x.z; S[i + 3] = x.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < E; i++) {
+            const int d = lane + kLanes * i;
+            S[i] = (j < V && d < D) ? scol[d] : 0.0f;
+        }
     }
     int stage = 0;
     for (int c0 = t0; c0 < t1; c0 += chunk, stage ^= 1) {
@@ -257,18 +270,41 @@ delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, 
             const float * qq = s_q + tt * Dp;
             const float * gg = s_g + tt * Dp;
             float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
+            float kk[E];                       // the key's entries of this lane, kept for the write
+            if (VEC) {
 #pragma unroll
-            for (int i = 0; i < E; i += 2) {
-                const int d = lane + kLanes * i;
-                if (d < D) {
-                    S[i] *= gg[d];
-                    a0 = fmaf(kq[d], S[i], a0);
-                    b0 = fmaf(qq[d], S[i], b0);
+                for (int i = 0; i < E; i += 4) {
+                    const int d = 4 * lane + 4 * kLanes * (i >> 2);
+                    float4 g4 = make_float4(1.0f, 1.0f, 1.0f, 1.0f), k4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), q4 = k4;
+                    if (d < D) {
+                        g4 = *reinterpret_cast<const float4 *>(gg + d);
+                        k4 = *reinterpret_cast<const float4 *>(kq + d);
+                        q4 = *reinterpret_cast<const float4 *>(qq + d);
+                    }
+                    kk[i] = k4.x; kk[i + 1] = k4.y; kk[i + 2] = k4.z; kk[i + 3] = k4.w;
+                    S[i] *= g4.x; S[i + 1] *= g4.y; S[i + 2] *= g4.z; S[i + 3] *= g4.w;
+                    a0 = fmaf(k4.x, S[i], a0);     b0 = fmaf(q4.x, S[i], b0);
+                    a1 = fmaf(k4.y, S[i + 1], a1); b1 = fmaf(q4.y, S[i + 1], b1);
+                    a0 = fmaf(k4.z, S[i + 2], a0); b0 = fmaf(q4.z, S[i + 2], b0);
+                    a1 = fmaf(k4.w, S[i + 3], a1); b1 = fmaf(q4.w, S[i + 3], b1);
                 }
-                if (d + kLanes < D) {
-                    S[i + 1] *= gg[d + kLanes];
-                    a1 = fmaf(kq[d + kLanes], S[i + 1], a1);
-                    b1 = fmaf(qq[d + kLanes], S[i + 1], b1);
+            } else {
+#pragma unroll
+                for (int i = 0; i < E; i += 2) {
+                    const int d = lane + kLanes * i;
+                    kk[i] = kk[i + 1] = 0.0f;
+                    if (d < D) {
+                        kk[i] = kq[d];
+                        S[i] *= gg[d];
+                        a0 = fmaf(kk[i], S[i], a0);
+                        b0 = fmaf(qq[d], S[i], b0);
+                    }
+                    if (d + kLanes < D) {
+                        kk[i + 1] = kq[d + kLanes];
+                        S[i + 1] *= gg[d + kLanes];
+                        a1 = fmaf(kk[i + 1], S[i + 1], a1);
+                        b1 = fmaf(qq[d + kLanes], S[i + 1], b1);
+                    }
                 }
             }
             float a = a0 + a1, b = b0 + b1;
@@ -279,19 +315,24 @@ delta_scan_kernel(const float * __restrict__ qn, const float * __restrict__ kn, 
             }
             const float u = s_b[2 * tt] * (s_v[tt * kCols + col] - a);
 #pragma unroll
-            for (int i = 0; i < E; i++) {
-                const int d = lane + kLanes * i;
-                if (d < D) S[i] = fmaf(kq[d], u, S[i]);
-            }
+            for (int i = 0; i < E; i++) S[i] = fmaf(kk[i], u, S[i]);        // (entries beyond D stay zero: their key is zero)
             if (lane == 0 && j < V) out[(size_t) (c0 + tt) * HV + h * V + j] = fmaf(s_b[2 * tt + 1], u, b);
         }
         __syncthreads();                       // everyone is done with this stage before it is filled again
     }
     if (j < V) {
+        if (VEC) {
 #pragma unroll
-        for (int i = 0; i < E; i++) {
-            const int d = lane + kLanes * i;
-            if (d < D) scol[d] = S[i];
+            for (int i = 0; i < E; i += 4) {
+                const int d = 4 * lane + 4 * kLanes * (i >> 2);
+                if (d < D) *reinterpret_cast<float4 *>(scol + d) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < E; i++) {
+                const int d = lane + kLanes * i;
+                if (d < D) scol[d] = S[i];
+            }
         }
     }
 }
@@ -332,14 +373,14 @@ template <int E, typename A>
 static int launch_scan(const float * qn, const float * kn, const float * vv, const float * beta, const float * decay,
                        const float * qk, float * state, long long state_stride, const A * proj, long long ld, int col_off,
                        int n_taps, const int * cu_q, const int * state_slots, float * out, int S, int H, int G, int D, int V,
-                       cudaStream_t stream) {
+                       int max_q_len, bool vec, cudaStream_t stream) {
     const int Dp = (D + 3) & ~3;
-    const int chunk = D <= 256 ? 16 : 8;       // tokens per stage of shared memory
+    int chunk = D <= 256 ? 16 : 8;             // tokens per stage of shared memory
+    if (max_q_len > 0 && max_q_len < chunk) chunk = max_q_len;         // single tokens: small stages, more CTAs per SM
     const size_t smem = (size_t) 2 * chunk * (3 * Dp + kCols + 4) * sizeof(float);
     if (smem > 200 * 1024) return IIAN_ERR_LIMIT;
-    const bool vec = D % 4 == 0 && (((uintptr_t) qn | (uintptr_t) kn | (uintptr_t) decay) & 15) == 0;
     const dim3 grid((V + kCols - 1) / kCols, H, S);
-    if (vec) {
+    if constexpr (E % 4 == 0) if (vec) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<E, true, A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         return iian_launch(delta_scan_kernel<E, true, A>, grid, dim3(kCols * kLanes), smem, stream, qn, kn, vv, beta, decay, qk, state,
                            state_stride, (long long) H * V * D, proj, ld, col_off, n_taps, cu_q, state_slots, out, H, G, D, V, chunk);
@@ -353,11 +394,13 @@ template <typename A>
 static int scan_by_depth(const float * qn, const float * kn, const float * vv, const float * beta, const float * decay,
                          const float * qk, float * state, long long state_stride, const A * proj, long long ld, int col_off,
                          int n_taps, const int * cu_q, const int * state_slots, float * out, int S, int H, int G, int D, int V,
-                         cudaStream_t stream) {
+                         int max_q_len, cudaStream_t stream) {
     const int e = (D + kLanes - 1) / kLanes;
+    const bool vec = D % 4 == 0 && state_stride % 4 == 0 &&
+                     (((uintptr_t) qn | (uintptr_t) kn | (uintptr_t) decay | (uintptr_t) state) & 15) == 0;
 #define IIAN_SCAN(E) return launch_scan<E, A>(qn, kn, vv, beta, decay, qk, state, state_stride, proj, ld, col_off, n_taps, cu_q, \
-                                              state_slots, out, S, H, G, D, V, stream)
-    if (e <= 2) IIAN_SCAN(2);
+                                              state_slots, out, S, H, G, D, V, max_q_len, vec, stream)
+    if (e <= 2 && !vec) IIAN_SCAN(2);
     if (e <= 4) IIAN_SCAN(4);
     if (e <= 8) IIAN_SCAN(8);
     if (e <= 16) IIAN_SCAN(16);
@@ -367,18 +410,19 @@ static int scan_by_depth(const float * qn, const float * kn, const float * vv, c
     return IIAN_ERR_LIMIT;
 }
 
-// out: float32 [N, H * V].  S sequences (grid z); a sequence with state slot -1 is padding.
+// out: float32 [N, H * V].  S sequences (grid z); a sequence with state slot -1 is padding.  max_q_len: the most tokens a
+// sequence has in this step (0: unknown); it sizes the stages of shared memory.
 IIAN_API int iian_delta_scan(const float * qn, const float * kn, const float * vv, const float * beta, const float * decay,
                              const float * qk, float * state, long long state_stride, const void * proj, long long ld,
                              int col_off, int act_dtype, int n_taps, const int * cu_q, const int * state_slots, float * out,
-                             int S, int H, int G, int D, int V, cudaStream_t stream) {
+                             int S, int H, int G, int D, int V, int max_q_len, cudaStream_t stream) {
     if (S <= 0) return IIAN_OK;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0 || n_taps < 1 || n_taps > kMaxTaps || S > 65535 || H > 65535) return IIAN_ERR_SHAPE;
     if (act_dtype == IIAN_F32)
         return scan_by_depth<float>(qn, kn, vv, beta, decay, qk, state, state_stride, (const float *) proj, ld, col_off, n_taps,
-                                    cu_q, state_slots, out, S, H, G, D, V, stream);
+                                    cu_q, state_slots, out, S, H, G, D, V, max_q_len, stream);
     if (act_dtype == IIAN_BF16)
         return scan_by_depth<__nv_bfloat16>(qn, kn, vv, beta, decay, qk, state, state_stride, (const __nv_bfloat16 *) proj, ld,
-                                            col_off, n_taps, cu_q, state_slots, out, S, H, G, D, V, stream);
+                                            col_off, n_taps, cu_q, state_slots, out, S, H, G, D, V, max_q_len, stream);
     return IIAN_ERR_DTYPE;
 }

@@ -10,6 +10,7 @@
 //
 // `A` is the activation type; sums, norms and the stream are float32.  A row's result depends on that row only.
 #include "common.cuh"
+#include <initializer_list>
 
 namespace iian {
 
@@ -54,6 +55,118 @@ __global__ void scaled_add_unit_rms_kernel(float * __restrict__ residual, const 
     const float inv = mult / sqrtf(ss / (float) H + eps);
     for (int i = threadIdx.x; i < H; i += blockDim.x)
         residual[base + i] = fmaf(to_f32(y[base + i]) * inv, weight[i], residual[base + i]);
+}
+
+// ---- the same with four entries per access and the row kept in registers between the two passes -------------------------
+// (H a multiple of 4, at most blockDim.x * 4 * KEEP entries, every pointer aligned to four entries)
+constexpr int kRowKeep = 4;
+
+__device__ __forceinline__ float4 load4(const float * p) { return *reinterpret_cast<const float4 *>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16 * p) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float * p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16 * p, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<unsigned *>(&a);
+    raw.y = *reinterpret_cast<unsigned *>(&b);
+    *reinterpret_cast<uint2 *>(p) = raw;
+}
+
+template <typename A>
+__global__ void scaled_add_rms_norm_vec_kernel(float * __restrict__ residual, const A * __restrict__ delta, float mult,
+                                               const float * __restrict__ weight, A * __restrict__ out, A * __restrict__ copy,
+                                               int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    float4 v[kRowKeep];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kRowKeep; k++) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        v[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < H) v[k] = load4(residual + base + i);
+    }
+    if (delta != nullptr) {
+#pragma unroll
+        for (int k = 0; k < kRowKeep; k++) {
+            const int i = 4 * (threadIdx.x + k * blockDim.x);
+            if (i < H) {
+                const float4 d = load4(delta + base + i);
+                v[k].x = fmaf(mult, d.x, v[k].x); v[k].y = fmaf(mult, d.y, v[k].y);
+                v[k].z = fmaf(mult, d.z, v[k].z); v[k].w = fmaf(mult, d.w, v[k].w);
+                store4(residual + base + i, v[k]);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kRowKeep; k++) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        if (i < H && copy != nullptr) store4(copy + base + i, v[k]);
+        ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss);
+        ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
+    }
+    if (out == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float) H + eps);
+#pragma unroll
+    for (int k = 0; k < kRowKeep; k++) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        if (i < H) {
+            const float4 w = load4(weight + i);
+            store4(out + base + i, make_float4(v[k].x * inv * w.x, v[k].y * inv * w.y, v[k].z * inv * w.z, v[k].w * inv * w.w));
+        }
+    }
+}
+
+template <typename A>
+__global__ void scaled_add_unit_rms_vec_kernel(float * __restrict__ residual, const A * __restrict__ y, float mult,
+                                               const float * __restrict__ weight, int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    float4 v[kRowKeep], r[kRowKeep], w[kRowKeep];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kRowKeep; k++) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        v[k] = r[k] = w[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < H) {
+            v[k] = load4(y + base + i);
+            r[k] = load4(residual + base + i);
+            w[k] = load4(weight + i);
+        }
+        ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss);
+        ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = mult / sqrtf(ss / (float) H + eps);
+#pragma unroll
+    for (int k = 0; k < kRowKeep; k++) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        if (i < H)
+            store4(residual + base + i, make_float4(fmaf(v[k].x * inv, w[k].x, r[k].x), fmaf(v[k].y * inv, w[k].y, r[k].y),
+                                                    fmaf(v[k].z * inv, w[k].z, r[k].z), fmaf(v[k].w * inv, w[k].w, r[k].w)));
+    }
+}
+
+// threads of a block for the vector forms, or 0: the row does not fit them (not a multiple of 4, too long, not aligned)
+static int row_vec_threads(int H, int elem_bytes, std::initializer_list<const void *> act_ptrs, std::initializer_list<const void *> f32_ptrs) {
+    if (H % 4 != 0 || H > 1024 * 4 * kRowKeep) return 0;
+    for (const void * p : act_ptrs) if ((uintptr_t) p % (4 * elem_bytes)) return 0;
+    for (const void * p : f32_ptrs) if ((uintptr_t) p % 16) return 0;
+    int t = 128;
+    while (t * 4 * kRowKeep < H) t *= 2;
+    // short rows: spread over more threads than one access each needs, so that a row's latency is one trip
+    while (t < 256 && t * 4 < H) t *= 2;
+    return t;
 }
 
 template <typename A>
@@ -107,6 +220,22 @@ __global__ void xielu_kernel(const A * __restrict__ x, const float * __restrict_
     out[e] = from_f32<A>(y);
 }
 
+// four entries per thread (total a multiple of 4, both pointers aligned to four entries)
+template <typename A>
+__global__ void xielu_vec_kernel(const A * __restrict__ x, const float * __restrict__ pq, A * __restrict__ out, long long quads) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long long e = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= quads) return;
+    const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
+    float4 z = load4(x + 4 * e);
+    z.x = z.x > 0.0f ? fmaf(ap * z.x, z.x, 0.5f * z.x) : fmaf(an, expm1f(z.x) - z.x, 0.5f * z.x);
+    z.y = z.y > 0.0f ? fmaf(ap * z.y, z.y, 0.5f * z.y) : fmaf(an, expm1f(z.y) - z.y, 0.5f * z.y);
+    z.z = z.z > 0.0f ? fmaf(ap * z.z, z.z, 0.5f * z.z) : fmaf(an, expm1f(z.z) - z.z, 0.5f * z.z);
+    z.w = z.w > 0.0f ? fmaf(ap * z.w, z.w, 0.5f * z.w) : fmaf(an, expm1f(z.w) - z.w, 0.5f * z.w);
+    store4(out + 4 * e, z);
+}
+
 __global__ void tanh_cap_kernel(float * __restrict__ x, float cap, long long total) {
     pdl_wait();
     pdl_launch_dependents();
@@ -124,6 +253,14 @@ IIAN_API int iian_scaled_add_rms_norm(float * residual, const void * delta, floa
                                       void * copy, int act_dtype, int N, int H, float eps, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
     if (H <= 0) return IIAN_ERR_SHAPE;
+    if (act_dtype != IIAN_F32 && act_dtype != IIAN_BF16) return IIAN_ERR_DTYPE;
+    if (const int vt = row_vec_threads(H, act_dtype == IIAN_F32 ? 4 : 2, {delta, out, copy}, {residual, weight})) {
+        if (act_dtype == IIAN_F32)
+            return iian_launch(scaled_add_rms_norm_vec_kernel<float>, dim3(N), dim3(vt), 0, stream, residual, (const float *) delta,
+                               mult, weight, (float *) out, (float *) copy, H, eps);
+        return iian_launch(scaled_add_rms_norm_vec_kernel<__nv_bfloat16>, dim3(N), dim3(vt), 0, stream, residual,
+                           (const __nv_bfloat16 *) delta, mult, weight, (__nv_bfloat16 *) out, (__nv_bfloat16 *) copy, H, eps);
+    }
     const int threads = H >= 1024 ? 256 : 128;
     if (act_dtype == IIAN_F32)
         return iian_launch(scaled_add_rms_norm_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float *) delta,
@@ -138,6 +275,14 @@ IIAN_API int iian_scaled_add_unit_rms(float * residual, const void * y, float mu
                                       int H, float eps, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
     if (H <= 0) return IIAN_ERR_SHAPE;
+    if (act_dtype != IIAN_F32 && act_dtype != IIAN_BF16) return IIAN_ERR_DTYPE;
+    if (const int vt = row_vec_threads(H, act_dtype == IIAN_F32 ? 4 : 2, {y}, {residual, weight})) {
+        if (act_dtype == IIAN_F32)
+            return iian_launch(scaled_add_unit_rms_vec_kernel<float>, dim3(N), dim3(vt), 0, stream, residual, (const float *) y, mult,
+                               weight, H, eps);
+        return iian_launch(scaled_add_unit_rms_vec_kernel<__nv_bfloat16>, dim3(N), dim3(vt), 0, stream, residual,
+                           (const __nv_bfloat16 *) y, mult, weight, H, eps);
+    }
     const int threads = H >= 1024 ? 256 : 128;
     if (act_dtype == IIAN_F32)
         return iian_launch(scaled_add_unit_rms_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float *) y, mult,
@@ -185,6 +330,15 @@ IIAN_API int iian_gelu_mul_table(const void * g, const void * table, int table_d
 IIAN_API int iian_xielu(const void * x, const float * pq, void * out, int act_dtype, long long total, cudaStream_t stream) {
     if (total <= 0) return IIAN_OK;
     const int threads = 256;
+    const int eb = act_dtype == IIAN_F32 ? 4 : 2;
+    if (total % 4 == 0 && (uintptr_t) x % (4 * eb) == 0 && (uintptr_t) out % (4 * eb) == 0 && (act_dtype == IIAN_F32 || act_dtype == IIAN_BF16)) {
+        const long long quads = total / 4;
+        const unsigned vb = (unsigned) ((quads + threads - 1) / threads);
+        if (act_dtype == IIAN_F32)
+            return iian_launch(xielu_vec_kernel<float>, dim3(vb), dim3(threads), 0, stream, (const float *) x, pq, (float *) out, quads);
+        return iian_launch(xielu_vec_kernel<__nv_bfloat16>, dim3(vb), dim3(threads), 0, stream, (const __nv_bfloat16 *) x, pq,
+                           (__nv_bfloat16 *) out, quads);
+    }
     const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
     if (act_dtype == IIAN_F32)
         return iian_launch(xielu_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float *) x, pq, (float *) out, total);

@@ -1568,10 +1568,10 @@ class CudaKernels:
                   decay.data_ptr(), qk.data_ptr(), n, h, g, d, v, _stream()), "delta_prep")
         fn = _fn("delta_rule", "iian_delta_scan",
                  [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int,
-                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+                  c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
         _check(fn(qn.data_ptr(), kn.data_ptr(), vv.data_ptr(), beta.data_ptr(), decay.data_ptr(), qk.data_ptr(), state.data_ptr(),
                   state.shape[1], pp, ld, col_off, code, n_taps, ctx.cu_q.data_ptr(), ctx.state_slots.data_ptr(),
-                  _cuda(out, "delta out", f32), s, h, g, d, v, _stream()), "delta_scan")
+                  _cuda(out, "delta out", f32), s, h, g, d, v, int(getattr(ctx, "max_q_len", 0) or 0), _stream()), "delta_scan")
 
     # ---- routing by a table, weights on the experts' outputs (csrc/moe.cu) ------------------------------------------------------
     def moe_table_route(self, tokens: torch.Tensor, rows: Optional[torch.Tensor], table: torch.Tensor, num_experts: int,
