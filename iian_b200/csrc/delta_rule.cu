@@ -92,19 +92,25 @@ delta_prep_kernel(const A * __restrict__ proj, long long ld, int col_off, int b_
             const float b = silu_f32(delta_conv(proj, ld, col_off + ck, (long long) t, first, tail, C, ck, taps, n_taps));
             act_q[d] = a;
             act_k[d] = b;
-            sq = fmaf(a, a, sq);
-            sk = fmaf(b, b, sk);
-            dot = fmaf(a, b, dot);
         }
-        sq = warp_sum(sq);
-        sk = warp_sum(sk);
-        dot = warp_sum(dot);
-        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-        if (lane == 0) { red[0][warp] = sq; red[1][warp] = sk; red[2][warp] = dot; }
+        // the three sums in the order the tiled kernel takes them (a lane over d = lane, lane + 32, ..., then the lanes), so
+        // that a token's vectors are the same bits whichever kernel prepared them
         __syncthreads();
-        sq = sk = dot = 0.0f;
-#pragma unroll
-        for (int w = 0; w < kPrepThreads / 32; w++) { sq += red[0][w]; sk += red[1][w]; dot += red[2][w]; }
+        if (threadIdx.x < 32) {
+            sq = sk = dot = 0.0f;
+            for (int d = threadIdx.x; d < D; d += 32) {
+                const float a = act_q[d], b = act_k[d];
+                sq = fmaf(a, a, sq);
+                sk = fmaf(b, b, sk);
+                dot = fmaf(a, b, dot);
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            dot = warp_sum(dot);
+            if (threadIdx.x == 0) { red[0][0] = sq; red[1][0] = sk; red[2][0] = dot; }
+        }
+        __syncthreads();
+        sq = red[0][0]; sk = red[1][0]; dot = red[2][0];
         const float iq = q_scale / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
         for (int d = threadIdx.x; d < D; d += kPrepThreads) {
             qn[t * GD + u * D + d] = act_q[d] * iq;
@@ -124,6 +130,127 @@ delta_prep_kernel(const A * __restrict__ proj, long long ld, int col_off, int b_
         decay[t * (size_t) (H * D) + e] = expf(-rate * softplus_f32(z[t * (size_t) (H * D) + e] + dt_bias[e]));
     }
     if (threadIdx.x == 0) beta[t * H + h] = 1.0f / (1.0f + expf(-to_f32(proj[t * ld + b_off + h])));
+}
+
+// The same preparation for steps of many tokens.  Grid (ceil(N / T), G + H): a CTA takes T neighbouring rows of the step for
+// one unit (a query/key head, or a value head with its decays and write strength).  The rows the convolution needs
+// (T + taps - 1 of them) and the unit's filters first go to shared memory, every load independent of the others, together with
+// the tokens' sequence numbers; then each warp takes tokens of its own, a lane the entries lane, lane + 32, ...  Inputs from
+// before a sequence's first row in the step come from the state's tail as in the kernel above.  Results are the same bits.
+// Shared memory: x [W][T + taps - 1] rows of the unit's W channels | filters [W][taps] | first [T] | slot [T] (ints).
+constexpr int kPrepTileWarps = 4;
+constexpr int kPrepTileFrom = 256;          // tokens in a step from which the tiled kernel runs (tiles of 8; of 16 from four times as many)
+constexpr int kPrepPerLane = kPrepMaxDim / 32;
+
+template <typename A>
+__global__ void __launch_bounds__(kPrepTileWarps * 32)
+delta_prep_tile_kernel(const A * __restrict__ proj, long long ld, int col_off, int b_off,
+                       const float * __restrict__ z, const float * __restrict__ taps, int n_taps,
+                       const float * __restrict__ a_log, const float * __restrict__ dt_bias,
+                       const float * __restrict__ state, long long state_stride, long long tail_off,
+                       const int * __restrict__ seq_of_token, const int * __restrict__ cu_q,
+                       const int * __restrict__ state_slots,
+                       float * __restrict__ qn, float * __restrict__ kn, float * __restrict__ vv,
+                       float * __restrict__ beta, float * __restrict__ decay, float * __restrict__ qk,
+                       int N, int T, int H, int G, int D, int V, float q_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    extern __shared__ __align__(16) float psm[];
+    const int u = blockIdx.y;
+    const int GD = G * D, HV = H * V, C = 2 * GD + HV, HD = H * D;
+    const int back = n_taps - 1, rows = T + back;
+    const bool qk_unit = u < G;
+    const int W = qk_unit ? 2 * D : V;                        // channels of this unit: q | k of a head, or a head's values
+    float * xs = psm;                                        // [rows][W]
+    float * ws = xs + (size_t) rows * W;                     // [W][n_taps]
+    int * first_s = reinterpret_cast<int *>(ws + (size_t) W * n_taps);
+    int * slot_s = first_s + T;
+    const long long t0 = (long long) blockIdx.x * T;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    // channel w of the unit is channel chan(w) of the convolution
+    auto chan = [&](int w) { return qk_unit ? (w < D ? u * D + w : GD + u * D + (w - D)) : 2 * GD + (u - G) * V + w; };
+    if (tid < T) {
+        const long long t = t0 + tid;
+        int first = 0, slot = -2;                            // -2: no token (beyond the step, or padding)
+        if (t < N) {
+            const int sq = seq_of_token[t];
+            if (sq >= 0) { first = cu_q[sq]; slot = state_slots[sq]; }
+        }
+        first_s[tid] = first;
+        slot_s[tid] = slot;
+    }
+    for (int i = tid; i < rows * W; i += nthr) {
+        const int ri = i / W, w = i - ri * W;
+        const long long r = t0 - back + ri;
+        xs[i] = r >= 0 && r < N ? to_f32(proj[(size_t) r * ld + col_off + chan(w)]) : 0.0f;
+    }
+    for (int i = tid; i < W * n_taps; i += nthr) {
+        const int w = i / n_taps, j = i - w * n_taps;
+        ws[i] = taps[(size_t) chan(w) * n_taps + j];
+    }
+    __syncthreads();
+    const int warp = tid >> 5, lane = tid & 31;
+    // the convolution of channel w (convolution channel c) at the tile's token ti
+    auto conv = [&](int ti, long long t, int first, const float * tail, int w, int c) {
+        float acc = 0.0f;
+        for (int j = 0; j < n_taps; j++) {
+            const long long r = t - back + j;
+            float x = 0.0f;
+            if (r >= first) x = xs[(size_t) (ti + j) * W + w];
+            else {
+                const int idx = (int) (r - first) + back;
+                if (tail != nullptr && idx >= 0) x = tail[(size_t) idx * C + c];
+            }
+            acc = fmaf(ws[w * n_taps + j], x, acc);
+        }
+        return acc;
+    };
+    for (int ti = warp; ti < T; ti += kPrepTileWarps) {
+        const int slot = slot_s[ti];
+        if (slot == -2) continue;
+        const long long t = t0 + ti;
+        const int first = first_s[ti];
+        const float * tail = slot >= 0 ? state + (size_t) slot * state_stride + tail_off : nullptr;
+        if (qk_unit) {
+            float aq[kPrepPerLane], ak[kPrepPerLane];
+            float sq = 0.0f, sk = 0.0f, dot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kPrepPerLane; i++) {
+                const int d = lane + 32 * i;
+                aq[i] = ak[i] = 0.0f;
+                if (d < D) {
+                    aq[i] = silu_f32(conv(ti, t, first, tail, d, u * D + d));
+                    ak[i] = silu_f32(conv(ti, t, first, tail, D + d, GD + u * D + d));
+                    sq = fmaf(aq[i], aq[i], sq);
+                    sk = fmaf(ak[i], ak[i], sk);
+                    dot = fmaf(aq[i], ak[i], dot);
+                }
+            }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            dot = warp_sum(dot);
+            const float iq = q_scale / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+#pragma unroll
+            for (int i = 0; i < kPrepPerLane; i++) {
+                const int d = lane + 32 * i;
+                if (d < D) {
+                    qn[t * GD + u * D + d] = aq[i] * iq;
+                    kn[t * GD + u * D + d] = ak[i] * ik;
+                }
+            }
+            if (lane == 0) qk[t * G + u] = dot * iq * ik;
+        } else {
+            const int h = u - G;
+            const float rate = expf(a_log[h]);
+            for (int d = lane; d < D; d += 32) {
+                const size_t e = (size_t) h * D + d;
+                decay[t * (size_t) HD + e] = expf(-rate * softplus_f32(z[t * (size_t) HD + e] + dt_bias[e]));
+            }
+            for (int j = lane; j < V; j += 32)
+                vv[t * HV + h * V + j] = silu_f32(conv(ti, t, first, tail, j, 2 * GD + h * V + j));
+            if (lane == 0) beta[t * H + h] = 1.0f / (1.0f + expf(-to_f32(proj[t * ld + b_off + h])));
+        }
+    }
 }
 
 constexpr int kCols = 16;        // columns of S a CTA owns
@@ -357,6 +484,30 @@ IIAN_API int iian_delta_prep(const void * proj, long long ld, int col_off, int b
     if (G + H > 65535) return IIAN_ERR_LIMIT;
     const long long tail_off = (long long) H * V * D;
     const float q_scale = 1.0f / sqrtf((float) D);
+    // many tokens: tiles of T rows through shared memory; few: a CTA per token and unit, so that they spread over the GPU
+    int T = N >= 4 * kPrepTileFrom ? 16 : N >= kPrepTileFrom ? 8 : 0;
+    size_t smem = 0;
+    const int W = 2 * D > V ? 2 * D : V;
+    for (; T >= 4; T /= 2) {
+        smem = ((size_t) (T + n_taps - 1) * W + (size_t) W * n_taps + 2 * T) * sizeof(float);
+        if (smem <= 96 * 1024) break;
+    }
+    if (T >= 4) {
+        const dim3 tgrid((N + T - 1) / T, G + H);
+        if (act_dtype == IIAN_F32) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+            return iian_launch(delta_prep_tile_kernel<float>, tgrid, dim3(kPrepTileWarps * 32), smem, stream, (const float *) proj, ld,
+                               col_off, b_off, z, taps, n_taps, a_log, dt_bias, state, state_stride, tail_off, seq_of_token, cu_q,
+                               state_slots, qn, kn, vv, beta, decay, qk, N, T, H, G, D, V, q_scale);
+        }
+        if (act_dtype == IIAN_BF16) {
+            if (smem > 48 * 1024) cudaFuncSetAttribute(delta_prep_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+            return iian_launch(delta_prep_tile_kernel<__nv_bfloat16>, tgrid, dim3(kPrepTileWarps * 32), smem, stream,
+                               (const __nv_bfloat16 *) proj, ld, col_off, b_off, z, taps, n_taps, a_log, dt_bias, state, state_stride,
+                               tail_off, seq_of_token, cu_q, state_slots, qn, kn, vv, beta, decay, qk, N, T, H, G, D, V, q_scale);
+        }
+        return IIAN_ERR_DTYPE;
+    }
     const dim3 grid(N, G + H);
     if (act_dtype == IIAN_F32)
         return iian_launch(delta_prep_kernel<float>, grid, dim3(kPrepThreads), 0, stream, (const float *) proj, ld, col_off, b_off, z,

@@ -220,20 +220,40 @@ __global__ void xielu_kernel(const A * __restrict__ x, const float * __restrict_
     out[e] = from_f32<A>(y);
 }
 
-// four entries per thread (total a multiple of 4, both pointers aligned to four entries)
+// exp(z) - 1 - z for z <= 0.  32-bit rows keep expm1f; bfloat16 rows take the fast exponent: near zero the result is
+// added to z / 2, far finer than the row's rounding.
+template <typename A> __device__ __forceinline__ float xielu_tail(float z) { return expm1f(z) - z; }
+template <> __device__ __forceinline__ float xielu_tail<__nv_bfloat16>(float z) { return __expf(z) - 1.0f - z; }
+
+template <typename A>
+__device__ __forceinline__ float4 xielu4(float4 z, float ap, float an) {
+    z.x = z.x > 0.0f ? fmaf(ap * z.x, z.x, 0.5f * z.x) : fmaf(an, xielu_tail<A>(z.x), 0.5f * z.x);
+    z.y = z.y > 0.0f ? fmaf(ap * z.y, z.y, 0.5f * z.y) : fmaf(an, xielu_tail<A>(z.y), 0.5f * z.y);
+    z.z = z.z > 0.0f ? fmaf(ap * z.z, z.z, 0.5f * z.z) : fmaf(an, xielu_tail<A>(z.z), 0.5f * z.z);
+    z.w = z.w > 0.0f ? fmaf(ap * z.w, z.w, 0.5f * z.w) : fmaf(an, xielu_tail<A>(z.w), 0.5f * z.w);
+    return z;
+}
+
+// four entries at a time (total a multiple of 4, both pointers aligned to four entries); a thread takes kXieluQuads quads a
+// block's width apart, all loads issued before the first use
+constexpr int kXieluQuads = 4;
 template <typename A>
 __global__ void xielu_vec_kernel(const A * __restrict__ x, const float * __restrict__ pq, A * __restrict__ out, long long quads) {
     pdl_wait();
     pdl_launch_dependents();
-    const long long e = (long long) blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= quads) return;
+    const long long e0 = (long long) blockIdx.x * blockDim.x * kXieluQuads + threadIdx.x;
+    float4 z[kXieluQuads];
+#pragma unroll
+    for (int i = 0; i < kXieluQuads; i++) {
+        const long long e = e0 + (long long) i * blockDim.x;
+        if (e < quads) z[i] = load4(x + 4 * e);
+    }
     const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
-    float4 z = load4(x + 4 * e);
-    z.x = z.x > 0.0f ? fmaf(ap * z.x, z.x, 0.5f * z.x) : fmaf(an, expm1f(z.x) - z.x, 0.5f * z.x);
-    z.y = z.y > 0.0f ? fmaf(ap * z.y, z.y, 0.5f * z.y) : fmaf(an, expm1f(z.y) - z.y, 0.5f * z.y);
-    z.z = z.z > 0.0f ? fmaf(ap * z.z, z.z, 0.5f * z.z) : fmaf(an, expm1f(z.z) - z.z, 0.5f * z.z);
-    z.w = z.w > 0.0f ? fmaf(ap * z.w, z.w, 0.5f * z.w) : fmaf(an, expm1f(z.w) - z.w, 0.5f * z.w);
-    store4(out + 4 * e, z);
+#pragma unroll
+    for (int i = 0; i < kXieluQuads; i++) {
+        const long long e = e0 + (long long) i * blockDim.x;
+        if (e < quads) store4(out + 4 * e, xielu4<A>(z[i], ap, an));
+    }
 }
 
 __global__ void tanh_cap_kernel(float * __restrict__ x, float cap, long long total) {
@@ -333,7 +353,7 @@ IIAN_API int iian_xielu(const void * x, const float * pq, void * out, int act_dt
     const int eb = act_dtype == IIAN_F32 ? 4 : 2;
     if (total % 4 == 0 && (uintptr_t) x % (4 * eb) == 0 && (uintptr_t) out % (4 * eb) == 0 && (act_dtype == IIAN_F32 || act_dtype == IIAN_BF16)) {
         const long long quads = total / 4;
-        const unsigned vb = (unsigned) ((quads + threads - 1) / threads);
+        const unsigned vb = (unsigned) ((quads + (long long) threads * kXieluQuads - 1) / ((long long) threads * kXieluQuads));
         if (act_dtype == IIAN_F32)
             return iian_launch(xielu_vec_kernel<float>, dim3(vb), dim3(threads), 0, stream, (const float *) x, pq, (float *) out, quads);
         return iian_launch(xielu_vec_kernel<__nv_bfloat16>, dim3(vb), dim3(threads), 0, stream, (const __nv_bfloat16 *) x, pq,

@@ -223,11 +223,32 @@ def _selectors(H, G, D, V, taps, g):
 @pytest.mark.parametrize("H, G, D, V, taps", [(4, 2, 12, 20, 4), (2, 2, 40, 8, 2), (4, 1, 64, 32, 3), (1, 1, 160, 16, 1), (2, 2, 128, 128, 3),
                                               (5, 5, 20, 12, 3), (1, 1, 8, 8, 8), (1, 1, 300, 6, 2), (6, 3, 32, 64, 4)])
 def test_delta_rule_cut_into_steps_with_slots_used_again(dtype, H, G, D, V, taps):
+    plan = [[(0, 0, 5), (1, 0, 1)], [(0, 5, 7)], [(0, 7, 8)], [(0, 8, 37)], [(2, 0, 2)], [(2, 2, 3)], [(2, 3, 12)]]
+    _delta_plan(dtype, H, G, D, V, taps, [37, 1, 12], plan)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H, G, D, V, taps", [(4, 2, 12, 20, 4), (2, 2, 128, 128, 3), (1, 1, 300, 6, 2), (6, 3, 32, 64, 4), (2, 1, 64, 32, 1)])
+@pytest.mark.parametrize("big", [(300, 270), (700, 590)])
+def test_delta_rule_steps_of_many_tokens(dtype, H, G, D, V, taps, big):
+    """Steps long enough for the preparation's tiled form (rows staged through shared memory), with a sequence that starts in
+    the middle of a tile, behind and ahead of short steps; in 32-bit the long steps give the bits the short ones give."""
+    a, b = big
+    plan = [[(0, 0, 3), (1, 0, 5)], [(0, 3, a), (2, 0, b)], [(2, b, b + 20)], [(0, a, a + 1), (2, b + 20, b + 21)]]
+    got = _delta_plan(dtype, H, G, D, V, taps, [a + 1, 5, b + 21], plan, slots=(2, 0, 1))
+    if dtype == "float32":
+        short = [[(0, 0, 3), (1, 0, 5)]] + [[(0, lo, min(lo + 100, a))] for lo in range(3, a, 100)] + \
+                [[(2, lo, min(lo + 90, b + 20))] for lo in range(0, b + 20, 90)] + [[(0, a, a + 1), (2, b + 20, b + 21)]]
+        again = _delta_plan(dtype, H, G, D, V, taps, [a + 1, 5, b + 21], short, compare=False, slots=(2, 0, 1))
+        for s in range(3):
+            assert torch.equal(got[s], again[s]), f"sequence {s}: long and short steps differ by {(got[s] - again[s]).abs().max()}"
+
+
+def _delta_plan(dtype, H, G, D, V, taps, lens, plan, compare=True, slots=(2, 0, 2)):
     g = torch.Generator().manual_seed(H * D + V + taps)
     t, off = _selectors(H, G, D, V, taps, g)
     mc = {"heads": H, "kv_heads": G, "dim": D, "vdim": V, "conv": taps}
     eps = 1e-5
-    lens = [37, 1, 12]
     n_state = K().delta_state_floats(H, G, D, V, taps)
     state = torch.full((3, n_state), 7.0, device=DEV)                                 # slots hold leftovers ...
     seqs, wants = [], []
@@ -237,12 +258,11 @@ def test_delta_rule_cut_into_steps_with_slots_used_again(dtype, H, G, D, V, taps
         gate = (torch.randn(L, H * V, generator=g) * 2).to(DT[dtype])
         seqs.append((proj, z, gate))
         h = torch.cat([proj.double(), z.double(), gate.double()], dim=1)
-        wants.append(plain.channel_delta(h, t, "", mc, eps, return_state=True))
+        wants.append(plain.channel_delta(h, t, "", mc, eps, return_state=True) if compare else None)
     conv_w = torch.cat([t["q.conv"], t["k.conv"], t["v.conv"]]).to(DEV)
     norm_w = t["norm"].repeat(H).to(DEV)
-    slots = [2, 0, 2]                                                                  # the third sequence inherits the first one's slot
+    # by default the third sequence inherits the first one's slot
     got = [[] for _ in lens]
-    plan = [[(0, 0, 5), (1, 0, 1)], [(0, 5, 7)], [(0, 7, 8)], [(0, 8, 37)], [(2, 0, 2)], [(2, 2, 3)], [(2, 3, 12)]]
     fresh = {0: True, 1: True, 2: True}
     bufs = {}
 
@@ -278,8 +298,11 @@ def test_delta_rule_cut_into_steps_with_slots_used_again(dtype, H, G, D, V, taps
         K().head_norm_gate(heads, norm_w, gate, normed, num_heads=H, eps=eps)
         for j, (s, lo, hi) in enumerate(step):
             got[s].append(normed[cu[j]:cu[j + 1]].cpu())
+    got = [torch.cat(x) for x in got]
+    if not compare:
+        return got
     for s in range(3):
-        close(torch.cat(got[s]), wants[s][0], dtype, f"sequence {s} of {H} heads {D} x {V}", rel16=1e-2, abs32=1e-4)
+        close(got[s], wants[s][0], dtype, f"sequence {s} of {H} heads {D} x {V}", rel16=1e-2, abs32=1e-4)
     # what the slots hold at the end: the matrices (a column is contiguous) and the convolution's last inputs
     for s in (1, 2):
         S, tail = wants[s][1]
@@ -287,6 +310,7 @@ def test_delta_rule_cut_into_steps_with_slots_used_again(dtype, H, G, D, V, taps
         close(held[: H * V * D].view(H, V, D), S.transpose(1, 2), "float32", f"state of sequence {s}", abs32=1e-4)
         if taps > 1:
             close(held[H * V * D:].view(taps - 1, -1), tail, "float32", f"convolution tail of sequence {s}", abs32=0.0)
+    return got
 
 
 # ---- whole models ---------------------------------------------------------------------------------------------------
