@@ -137,7 +137,7 @@ delta_prep_kernel(const A * __restrict__ proj, long long ld, int col_off, int b_
 // (T + taps - 1 of them) and the unit's filters first go to shared memory, every load independent of the others, together with
 // the tokens' sequence numbers; then each warp takes tokens of its own, a lane the entries lane, lane + 32, ...  Inputs from
 // before a sequence's first row in the step come from the state's tail as in the kernel above.  Results are the same bits.
-// Shared memory: x [W][T + taps - 1] rows of the unit's W channels | filters [W][taps] | first [T] | slot [T] (ints).
+// Shared memory: x [T + taps - 1][W] rows of the unit's W channels | filters [taps][W] | first [T] | slot [T] (ints).
 constexpr int kPrepTileWarps = 4;
 constexpr int kPrepTileFrom = 256;          // tokens in a step from which the tiled kernel runs (tiles of 8; of 16 from four times as many)
 constexpr int kPrepPerLane = kPrepMaxDim / 32;
@@ -162,7 +162,7 @@ delta_prep_tile_kernel(const A * __restrict__ proj, long long ld, int col_off, i
     const bool qk_unit = u < G;
     const int W = qk_unit ? 2 * D : V;                        // channels of this unit: q | k of a head, or a head's values
     float * xs = psm;                                        // [rows][W]
-    float * ws = xs + (size_t) rows * W;                     // [W][n_taps]
+    float * ws = xs + (size_t) rows * W;                     // [n_taps][W]
     int * first_s = reinterpret_cast<int *>(ws + (size_t) W * n_taps);
     int * slot_s = first_s + T;
     const long long t0 = (long long) blockIdx.x * T;
@@ -179,29 +179,33 @@ delta_prep_tile_kernel(const A * __restrict__ proj, long long ld, int col_off, i
         first_s[tid] = first;
         slot_s[tid] = slot;
     }
-    for (int i = tid; i < rows * W; i += nthr) {
-        const int ri = i / W, w = i - ri * W;
-        const long long r = t0 - back + ri;
-        xs[i] = r >= 0 && r < N ? to_f32(proj[(size_t) r * ld + col_off + chan(w)]) : 0.0f;
-    }
-    for (int i = tid; i < W * n_taps; i += nthr) {
-        const int w = i / n_taps, j = i - w * n_taps;
-        ws[i] = taps[(size_t) chan(w) * n_taps + j];
+    for (int w = tid; w < W; w += nthr) {
+        const int c = chan(w);
+        const A * src = proj + col_off + c;
+        for (int ri = 0; ri < rows; ri++) {
+            const long long r = t0 - back + ri;
+            xs[ri * W + w] = r >= 0 && r < N ? to_f32(src[(size_t) r * ld]) : 0.0f;
+        }
+        for (int j = 0; j < n_taps; j++) ws[j * W + w] = taps[(size_t) c * n_taps + j];      // [taps][W]: lanes read neighbours
     }
     __syncthreads();
     const int warp = tid >> 5, lane = tid & 31;
-    // the convolution of channel w (convolution channel c) at the tile's token ti
-    auto conv = [&](int ti, long long t, int first, const float * tail, int w, int c) {
+    // the convolution of channel w (convolution channel c) at the tile's token ti; `before` of its inputs lie ahead of the
+    // sequence's first row in this step and come from the state's tail (or are zero)
+    auto conv = [&](int ti, int before, const float * tail, int w, int c) {
         float acc = 0.0f;
+        if (before <= 0) {
+            for (int j = 0; j < n_taps; j++) acc = fmaf(ws[j * W + w], xs[(ti + j) * W + w], acc);
+            return acc;
+        }
         for (int j = 0; j < n_taps; j++) {
-            const long long r = t - back + j;
             float x = 0.0f;
-            if (r >= first) x = xs[(size_t) (ti + j) * W + w];
+            if (j >= before) x = xs[(ti + j) * W + w];
             else {
-                const int idx = (int) (r - first) + back;
+                const int idx = j - before + back;             // place in the tail: rows first - back .. first - 1
                 if (tail != nullptr && idx >= 0) x = tail[(size_t) idx * C + c];
             }
-            acc = fmaf(ws[w * n_taps + j], x, acc);
+            acc = fmaf(ws[j * W + w], x, acc);
         }
         return acc;
     };
@@ -209,7 +213,7 @@ delta_prep_tile_kernel(const A * __restrict__ proj, long long ld, int col_off, i
         const int slot = slot_s[ti];
         if (slot == -2) continue;
         const long long t = t0 + ti;
-        const int first = first_s[ti];
+        const int before = (int) (first_s[ti] - (t - back));        // inputs of this token that lie ahead of the step's rows
         const float * tail = slot >= 0 ? state + (size_t) slot * state_stride + tail_off : nullptr;
         if (qk_unit) {
             float aq[kPrepPerLane], ak[kPrepPerLane];
@@ -219,8 +223,8 @@ delta_prep_tile_kernel(const A * __restrict__ proj, long long ld, int col_off, i
                 const int d = lane + 32 * i;
                 aq[i] = ak[i] = 0.0f;
                 if (d < D) {
-                    aq[i] = silu_f32(conv(ti, t, first, tail, d, u * D + d));
-                    ak[i] = silu_f32(conv(ti, t, first, tail, D + d, GD + u * D + d));
+                    aq[i] = silu_f32(conv(ti, before, tail, d, u * D + d));
+                    ak[i] = silu_f32(conv(ti, before, tail, D + d, GD + u * D + d));
                     sq = fmaf(aq[i], aq[i], sq);
                     sk = fmaf(ak[i], ak[i], sk);
                     dot = fmaf(aq[i], ak[i], dot);
@@ -247,7 +251,7 @@ delta_prep_tile_kernel(const A * __restrict__ proj, long long ld, int col_off, i
                 decay[t * (size_t) HD + e] = expf(-rate * softplus_f32(z[t * (size_t) HD + e] + dt_bias[e]));
             }
             for (int j = lane; j < V; j += 32)
-                vv[t * HV + h * V + j] = silu_f32(conv(ti, t, first, tail, j, 2 * GD + h * V + j));
+                vv[t * HV + h * V + j] = silu_f32(conv(ti, before, tail, j, 2 * GD + h * V + j));
             if (lane == 0) beta[t * H + h] = 1.0f / (1.0f + expf(-to_f32(proj[t * ld + b_off + h])));
         }
     }
