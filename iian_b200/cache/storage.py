@@ -20,7 +20,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts.base import KVNeed, RowNeed, StateNeed, is_paged
+from ..parts.base import MEMBER_STRIDE, KVNeed, RowNeed, StateNeed, is_paged, member_cache_id
 from .manager import PageGroup
 
 
@@ -71,6 +71,7 @@ class CacheStorage:
         self.dtype = dtype
         self.device = device
         self._views: Dict[int, object] = {}
+        self._members: Dict[int, tuple] = {}
         self.kv: List[torch.Tensor] = []
         self.states: Dict[int, torch.Tensor] = {}
         self.bytes = 0
@@ -106,7 +107,22 @@ class CacheStorage:
                 self._views[cid] = StateView(state=t)
 
     def view(self, cache_id: int):
-        return self._views.get(cache_id)
+        """What the call that works on ``cache_id`` gets: a view, None, or -- for a mixer made of several, whose members'
+        caches are filed under ``member_cache_id(cache_id, j)`` -- a tuple of views (None for a member without a cache)."""
+        v = self._views.get(cache_id)
+        if v is None and cache_id < MEMBER_STRIDE:
+            members = self._members.get(cache_id)
+            if members is None:
+                found = {}
+                j = 0
+                while j < 16:
+                    mv = self._views.get(member_cache_id(cache_id, j))
+                    if mv is not None:
+                        found[j] = mv
+                    j += 1
+                members = self._members[cache_id] = tuple(found.get(j) for j in range(max(found) + 1)) if found else ()
+            return members or None
+        return v
 
     def zero_state(self, slots: Sequence[int]) -> None:
         if not slots or not self.states:

@@ -81,7 +81,7 @@ def get_architecture(name: str) -> Architecture:
 
 def _load_builtin() -> None:
     # importing the module registers the plug-in
-    from ..models import galodra, lekilix, qwen3, senadra  # noqa: F401
+    from ..models import galodra, lekilix, nogelorn, qwen3, senadra  # noqa: F401
 
 
 def read_config_json(model_dir: str) -> Dict[str, Any]:

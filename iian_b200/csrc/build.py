@@ -31,7 +31,8 @@ SHARED_HEADERS = ["common.cuh"]
 # every library of the engine; build_all() compiles them all
 SOURCES = ["elementwise", "rope_kv", "attention_generic", "gemm_simt", "sampling", "gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05",
            "attention_tc", "gemm_stream", "postnorm", "latent_attention", "moe", "latent_attention_mma",
-           "stream_ops", "shared_kv", "matrix_memory", "residual_ops", "chunked_attention", "delta_rule"]
+           "stream_ops", "shared_kv", "matrix_memory", "residual_ops", "chunked_attention", "delta_rule", "window_attention",
+           "decay_scan"]
 # libraries only the bfloat16 serving path uses
 BF16_SOURCES: List[str] = ["gemm_skinny", "attention_mma", "prefetch", "gemm_tcgen05", "attention_tc", "gemm_stream"]
 BF16_PRODUCT_SOURCES: List[str] = ["gemm_skinny", "gemm_tcgen05", "gemm_stream"]

@@ -17,8 +17,10 @@ namespace iian {
 constexpr int kTileM = 64, kTileN = 64, kTileK = 16;
 
 // One warp per token.  ids / wts: [N, top].
+// mode 0: the weight of a chosen expert is sigmoid(logit); mode 1: the softmax over the chosen logits only.  bias (optional,
+// float32 [E]) is added to the logits before anything else.
 __global__ void moe_route_kernel(const float * __restrict__ logits, long long ld, int E, int top, int * __restrict__ ids,
-                                 float * __restrict__ wts, int N) {
+                                 float * __restrict__ wts, int N, const float * __restrict__ bias, int mode) {
     pdl_wait();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -31,7 +33,7 @@ __global__ void moe_route_kernel(const float * __restrict__ logits, long long ld
         int best_e = 0x7fffffff;
         for (int e = lane, i = 0; e < E; e += 32, i++) {
             if (i < 64 && ((taken_lo >> i) & 1ull)) continue;
-            const float v = z[e];
+            const float v = bias != nullptr ? z[e] + bias[e] : z[e];
             if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
         }
 #pragma unroll
@@ -43,8 +45,18 @@ __global__ void moe_route_kernel(const float * __restrict__ logits, long long ld
         if (best_e != 0x7fffffff && (best_e & 31) == lane) taken_lo |= 1ull << (best_e >> 5);
         if (lane == 0) {
             ids[t * top + k] = best_e == 0x7fffffff ? 0 : best_e;
-            wts[t * top + k] = best_e == 0x7fffffff ? 0.0f : 1.0f / (1.0f + expf(-best));
+            wts[t * top + k] = best_e == 0x7fffffff ? (mode == 1 ? -INFINITY : 0.0f) : mode == 1 ? best : 1.0f / (1.0f + expf(-best));
         }
+    }
+    if (mode == 1 && lane == 0) {      // the chosen logits came in falling order: the first is their maximum
+        const float mx = wts[t * top];
+        float sum = 0.0f;
+        for (int k = 0; k < top; k++) {
+            const float e = expf(wts[t * top + k] - mx);
+            wts[t * top + k] = e;
+            sum += e;
+        }
+        for (int k = 0; k < top; k++) wts[t * top + k] /= sum;
     }
 }
 
@@ -115,7 +127,7 @@ __global__ void moe_scatter_kernel(const A * __restrict__ h, const int * __restr
 // out[t, :] = sum_k [wts[t, k] *] ys[pos[t * top + k], :]  (k ascending)
 template <typename A>
 __global__ void moe_combine_kernel(const A * __restrict__ ys, const int * __restrict__ pos, const float * __restrict__ wts,
-                                   A * __restrict__ out, int W, int top) {
+                                   A * __restrict__ out, int W, int top, const A * add) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t t = blockIdx.x;
@@ -125,6 +137,7 @@ __global__ void moe_combine_kernel(const A * __restrict__ ys, const int * __rest
             const float y = to_f32(ys[(size_t) pos[t * top + k] * W + c]);
             acc += wts != nullptr ? wts[t * top + k] * y : y;
         }
+        if (add != nullptr) acc += to_f32(add[t * W + c]);        // may be `out` itself: read before it is written
         out[t * W + c] = from_f32<A>(acc);
     }
 }
@@ -232,7 +245,18 @@ IIAN_API int iian_moe_route(const float * logits, long long ld, int E, int top, 
     if (N <= 0) return IIAN_OK;
     if (E <= 0 || top <= 0 || top > E || E > 2048) return IIAN_ERR_SHAPE;
     const int warps = 4;
-    return iian_launch(moe_route_kernel, dim3((N + warps - 1) / warps), dim3(warps * 32), 0, stream, logits, ld, E, top, ids, wts, N);
+    return iian_launch(moe_route_kernel, dim3((N + warps - 1) / warps), dim3(warps * 32), 0, stream, logits, ld, E, top, ids, wts, N,
+                       (const float *) nullptr, 0);
+}
+
+// The same with a bias on the logits (float32 [E] or null) and the weights as the softmax over the chosen logits only.
+IIAN_API int iian_moe_route_softmax(const float * logits, long long ld, const float * bias, int E, int top, int * ids, float * wts,
+                                    int N, cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (E <= 0 || top <= 0 || top > E || E > 2048) return IIAN_ERR_SHAPE;
+    const int warps = 4;
+    return iian_launch(moe_route_kernel, dim3((N + warps - 1) / warps), dim3(warps * 32), 0, stream, logits, ld, E, top, ids, wts, N,
+                       bias, 1);
 }
 
 // tokens i32 [n_tokens], rows i32 [N] or null (then N == n_tokens), table i32 [V, top] -> ids i32 [N, top], wts f32 [N, top]
@@ -264,14 +288,20 @@ IIAN_API int iian_moe_scatter(const void * h, const int * pos, const float * wts
     return IIAN_ERR_DTYPE;
 }
 
-// wts: f32 [N, top], the weight of each expert's OUTPUT in the sum, or null (plain sum)
-IIAN_API int iian_moe_combine_weighted(const void * ys, const int * pos, const float * wts, void * out, int act_dtype, int N, int W,
-                                       int top, cudaStream_t stream) {
+// wts: f32 [N, top], the weight of each expert's OUTPUT in the sum, or null (plain sum); add: A [N, W] or null, rows added
+// after the experts' sum (an expert every token uses); it may be `out`.
+IIAN_API int iian_moe_combine_add(const void * ys, const int * pos, const float * wts, const void * add, void * out, int act_dtype,
+                                  int N, int W, int top, cudaStream_t stream) {
     if (N <= 0) return IIAN_OK;
     const int threads = W >= 1024 ? 256 : 128;
-    if (act_dtype == IIAN_F32) return iian_launch(moe_combine_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) ys, pos, wts, (float *) out, W, top);
-    if (act_dtype == IIAN_BF16) return iian_launch(moe_combine_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) ys, pos, wts, (__nv_bfloat16 *) out, W, top);
+    if (act_dtype == IIAN_F32) return iian_launch(moe_combine_kernel<float>, dim3(N), dim3(threads), 0, stream, (const float *) ys, pos, wts, (float *) out, W, top, (const float *) add);
+    if (act_dtype == IIAN_BF16) return iian_launch(moe_combine_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, (const __nv_bfloat16 *) ys, pos, wts, (__nv_bfloat16 *) out, W, top, (const __nv_bfloat16 *) add);
     return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_moe_combine_weighted(const void * ys, const int * pos, const float * wts, void * out, int act_dtype, int N, int W,
+                                       int top, cudaStream_t stream) {
+    return iian_moe_combine_add(ys, pos, wts, nullptr, out, act_dtype, N, W, top, stream);
 }
 
 IIAN_API int iian_moe_combine(const void * ys, const int * pos, void * out, int act_dtype, int N, int W, int top, cudaStream_t stream) {

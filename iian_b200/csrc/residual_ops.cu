@@ -7,6 +7,8 @@
 //   rms_norm_rows         out = x / sqrt(mean(x^2) + eps) * w for rows x of a wider matrix (row stride ld)
 //   xielu                 z > 0: softplus(p) z^2 + z / 2;  else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
 //   tanh_cap              z <- cap * tanh(z / cap), in place
+//   normed_add_rms_norm   x += y / sqrt(mean(y^2) + eps_y) * u [+ e]  (a sub-layer output that passes a norm of its own before
+//                         it joins the stream; e: a second float32 addend);  out = x / sqrt(mean(x^2) + eps) * w    (each optional)
 //
 // `A` is the activation type; sums, norms and the stream are float32.  A row's result depends on that row only.
 #include "common.cuh"
@@ -263,6 +265,106 @@ __global__ void tanh_cap_kernel(float * __restrict__ x, float cap, long long tot
     if (e < total) x[e] = cap * tanhf(x[e] / cap);
 }
 
+// ---- a normalised addend, then the next norm: both of a row in one pass over registers -----------------------------------
+// y (optional), u (optional: without it y is added as it is), e (optional float32 rows), w / out (optional)
+template <typename A>
+__global__ void normed_add_rms_norm_kernel(float * __restrict__ residual, const A * __restrict__ y, const float * __restrict__ u,
+                                           float eps_y, const float * __restrict__ extra, const float * __restrict__ weight,
+                                           A * __restrict__ out, int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    float * r = residual + base;
+    float inv_y = 1.0f;
+    if (y != nullptr && u != nullptr) {
+        float sy = 0.0f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = to_f32(y[base + i]);
+            sy = fmaf(v, v, sy);
+        }
+        sy = block_sum(sy, scratch);
+        inv_y = 1.0f / sqrtf(sy / (float) H + eps_y);
+    }
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (y != nullptr) v += u != nullptr ? to_f32(y[base + i]) * inv_y * u[i] : to_f32(y[base + i]);
+        if (extra != nullptr) v += extra[base + i];
+        r[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (out == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float) H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[base + i] = from_f32<A>(r[i] * inv * weight[i]);
+}
+
+template <typename A>
+__global__ void normed_add_rms_norm_vec_kernel(float * __restrict__ residual, const A * __restrict__ y, const float * __restrict__ u,
+                                               float eps_y, const float * __restrict__ extra, const float * __restrict__ weight,
+                                               A * __restrict__ out, int H, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const size_t base = (size_t) blockIdx.x * H;
+    float4 v[kRowKeep], a[kRowKeep];
+#pragma unroll
+    for (int k = 0; k < kRowKeep; k++) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        v[k] = a[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < H) {
+            v[k] = load4(residual + base + i);
+            if (y != nullptr) a[k] = load4(y + base + i);
+        }
+    }
+    if (y != nullptr && u != nullptr) {
+        float sy = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kRowKeep; k++) {
+            sy = fmaf(a[k].x, a[k].x, sy); sy = fmaf(a[k].y, a[k].y, sy);
+            sy = fmaf(a[k].z, a[k].z, sy); sy = fmaf(a[k].w, a[k].w, sy);
+        }
+        sy = block_sum(sy, scratch);
+        const float inv_y = 1.0f / sqrtf(sy / (float) H + eps_y);
+#pragma unroll
+        for (int k = 0; k < kRowKeep; k++) {
+            const int i = 4 * (threadIdx.x + k * blockDim.x);
+            if (i < H) {
+                const float4 w4 = load4(u + i);
+                a[k].x = a[k].x * inv_y * w4.x; a[k].y = a[k].y * inv_y * w4.y;
+                a[k].z = a[k].z * inv_y * w4.z; a[k].w = a[k].w * inv_y * w4.w;
+            }
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kRowKeep; k++) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        if (i < H) {
+            v[k].x += a[k].x; v[k].y += a[k].y; v[k].z += a[k].z; v[k].w += a[k].w;
+            if (extra != nullptr) {
+                const float4 e4 = load4(extra + base + i);
+                v[k].x += e4.x; v[k].y += e4.y; v[k].z += e4.z; v[k].w += e4.w;
+            }
+            if (y != nullptr || extra != nullptr) store4(residual + base + i, v[k]);
+        }
+        ss = fmaf(v[k].x, v[k].x, ss); ss = fmaf(v[k].y, v[k].y, ss);
+        ss = fmaf(v[k].z, v[k].z, ss); ss = fmaf(v[k].w, v[k].w, ss);
+    }
+    if (out == nullptr) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float) H + eps);
+#pragma unroll
+    for (int k = 0; k < kRowKeep; k++) {
+        const int i = 4 * (threadIdx.x + k * blockDim.x);
+        if (i < H) {
+            const float4 w4 = load4(weight + i);
+            store4(out + base + i, make_float4(v[k].x * inv * w4.x, v[k].y * inv * w4.y, v[k].z * inv * w4.z, v[k].w * inv * w4.w));
+        }
+    }
+}
+
 }  // namespace iian
 
 using namespace iian;
@@ -374,4 +476,27 @@ IIAN_API int iian_tanh_cap(float * x, float cap, long long total, cudaStream_t s
     const int threads = 256;
     const unsigned blocks = (unsigned) ((total + threads - 1) / threads);
     return iian_launch(tanh_cap_kernel, dim3(blocks), dim3(threads), 0, stream, x, cap, total);
+}
+
+// residual: f32 [N, H] in place; y: A [N, H] or null; u: f32 [H] or null (y joins the stream as it is); extra: f32 [N, H] or
+// null; weight f32 [H] and out A [N, H]: both or neither.
+IIAN_API int iian_normed_add_rms_norm(float * residual, const void * y, const float * u, float eps_y, const float * extra,
+                                      const float * weight, void * out, int act_dtype, int N, int H, float eps,
+                                      cudaStream_t stream) {
+    if (N <= 0) return IIAN_OK;
+    if (H <= 0 || (out != nullptr && weight == nullptr)) return IIAN_ERR_SHAPE;
+    if (act_dtype != IIAN_F32 && act_dtype != IIAN_BF16) return IIAN_ERR_DTYPE;
+    if (const int vt = row_vec_threads(H, act_dtype == IIAN_F32 ? 4 : 2, {y, out}, {residual, u, extra, weight})) {
+        if (act_dtype == IIAN_F32)
+            return iian_launch(normed_add_rms_norm_vec_kernel<float>, dim3(N), dim3(vt), 0, stream, residual, (const float *) y, u,
+                               eps_y, extra, weight, (float *) out, H, eps);
+        return iian_launch(normed_add_rms_norm_vec_kernel<__nv_bfloat16>, dim3(N), dim3(vt), 0, stream, residual,
+                           (const __nv_bfloat16 *) y, u, eps_y, extra, weight, (__nv_bfloat16 *) out, H, eps);
+    }
+    const int threads = H >= 1024 ? 256 : 128;
+    if (act_dtype == IIAN_F32)
+        return iian_launch(normed_add_rms_norm_kernel<float>, dim3(N), dim3(threads), 0, stream, residual, (const float *) y, u,
+                           eps_y, extra, weight, (float *) out, H, eps);
+    return iian_launch(normed_add_rms_norm_kernel<__nv_bfloat16>, dim3(N), dim3(threads), 0, stream, residual,
+                       (const __nv_bfloat16 *) y, u, eps_y, extra, weight, (__nv_bfloat16 *) out, H, eps);
 }

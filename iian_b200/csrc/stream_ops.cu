@@ -45,7 +45,7 @@ __global__ void sigmoid_mul_kernel(const A * __restrict__ x, const A * __restric
 // one warp per (token, head)
 template <typename A>
 __global__ void head_norm_gate_kernel(const float * __restrict__ x, const float * __restrict__ w, const A * __restrict__ g,
-                                      long long ld_g, A * __restrict__ out, long long items, int heads, int dv, float eps) {
+                                      long long ld_g, A * __restrict__ out, long long items, int heads, int dv, float eps, int gate_act) {
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long) blockIdx.x * (blockDim.x >> 5) + warp;
@@ -59,9 +59,21 @@ __global__ void head_norm_gate_kernel(const float * __restrict__ x, const float 
     const float inv = rsqrtf(ss / (float) dv + eps);
     for (int d = lane; d < dv; d += 32) {
         float v = xr[d] * inv * w[h * dv + d];
-        if (g != nullptr) v *= sigmoid_f32(to_f32(g[t * ld_g + h * dv + d]));
+        if (g != nullptr) {
+            const float z = to_f32(g[t * ld_g + h * dv + d]);
+            v *= gate_act == 1 ? z * sigmoid_f32(z) : sigmoid_f32(z);
+        }
         out[item * dv + d] = from_f32<A>(v);
     }
+}
+
+template <typename A>
+__global__ void weighted_sum2_kernel(const A * __restrict__ x, float a, const A * __restrict__ y, float b, A * __restrict__ out,
+                                     long long total) {
+    pdl_wait();
+    const long long idx = (long long) blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    out[idx] = from_f32<A>(fmaf(a, to_f32(x[idx]), b * to_f32(y[idx])));
 }
 
 }  // namespace iian
@@ -91,15 +103,31 @@ IIAN_API int iian_sigmoid_mul(const void * x, const void * g, long long ld_g, vo
     return IIAN_ERR_DTYPE;
 }
 
-// x: f32 [N, heads, dv]; w: f32 [heads * dv]; g: A rows of heads * dv with row stride ld_g, or null; out: A [N, heads * dv]
-IIAN_API int iian_head_norm_gate(const float * x, const float * w, const void * g, long long ld_g, void * out, int act_dtype,
-                                 int N, int heads, int dv, float eps, cudaStream_t stream) {
+// x: f32 [N, heads, dv]; w: f32 [heads * dv]; g: A rows of heads * dv with row stride ld_g, or null; out: A [N, heads * dv].
+// gate_act: what the gate's column passes before it multiplies: 0 sigmoid, 1 silu.
+IIAN_API int iian_head_norm_gate_act(const float * x, const float * w, const void * g, long long ld_g, void * out, int act_dtype,
+                                     int N, int heads, int dv, float eps, int gate_act, cudaStream_t stream) {
     const long long items = (long long) N * heads;
     if (items <= 0) return IIAN_OK;
-    if (dv <= 0) return IIAN_ERR_SHAPE;
+    if (dv <= 0 || (gate_act != 0 && gate_act != 1)) return IIAN_ERR_SHAPE;
     const int warps = 4;
     const unsigned blocks = (unsigned) ((items + warps - 1) / warps);
-    if (act_dtype == IIAN_F32) return iian_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, x, w, (const float *) g, ld_g, (float *) out, items, heads, dv, eps);
-    if (act_dtype == IIAN_BF16) return iian_launch(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, stream, x, w, (const __nv_bfloat16 *) g, ld_g, (__nv_bfloat16 *) out, items, heads, dv, eps);
+    if (act_dtype == IIAN_F32) return iian_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, x, w, (const float *) g, ld_g, (float *) out, items, heads, dv, eps, gate_act);
+    if (act_dtype == IIAN_BF16) return iian_launch(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), 0, stream, x, w, (const __nv_bfloat16 *) g, ld_g, (__nv_bfloat16 *) out, items, heads, dv, eps, gate_act);
+    return IIAN_ERR_DTYPE;
+}
+
+IIAN_API int iian_head_norm_gate(const float * x, const float * w, const void * g, long long ld_g, void * out, int act_dtype,
+                                 int N, int heads, int dv, float eps, cudaStream_t stream) {
+    return iian_head_norm_gate_act(x, w, g, ld_g, out, act_dtype, N, heads, dv, eps, 0, stream);
+}
+
+// out = a * x + b * y, element by element (x, y, out: A, same shape; the sum in float32)
+IIAN_API int iian_weighted_sum2(const void * x, float a, const void * y, float b, void * out, int act_dtype, long long total,
+                                cudaStream_t stream) {
+    if (total <= 0) return IIAN_OK;
+    const unsigned blocks = (unsigned) ((total + 255) / 256);
+    if (act_dtype == IIAN_F32) return iian_launch(weighted_sum2_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float *) x, a, (const float *) y, b, (float *) out, total);
+    if (act_dtype == IIAN_BF16) return iian_launch(weighted_sum2_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16 *) x, a, (const __nv_bfloat16 *) y, b, (__nv_bfloat16 *) out, total);
     return IIAN_ERR_DTYPE;
 }

@@ -132,23 +132,22 @@ class Model:
 
     # ---- what the caches must provide -----------------------------------------------------
     def cache_needs(self) -> Dict[int, object]:
-        """cache id -> KVNeed | StateNeed, taken from the mixer of the call that writes it."""
+        """cache id -> KVNeed | RowNeed | StateNeed, taken from the mixer of the call that writes it (a mixer made of several
+        answers with a tuple of needs; its members' caches appear under ``member_cache_id(cache, j)``)."""
         needs: Dict[int, object] = {}
 
         def need_of(block):
             return block.cache_need() if hasattr(block, "cache_need") else block.mixer.cache_need()
 
+        from ..parts.base import flatten_needs
         for call in self.spec.order:
-            need = need_of(self.blocks[call.layer])
-            if need is None:
-                continue
             if call.writes_cache:
-                needs[call.cache] = need
+                needs.update(flatten_needs(call.cache, need_of(self.blocks[call.layer])))
         for call in self.spec.order:
             if not call.writes_cache:
-                need = need_of(self.blocks[call.layer])
-                if need is not None and needs.get(call.cache) != need:
-                    raise ValueError(f"layer {call.layer} reads cache {call.cache}, whose owner stores something else")
+                for cid, need in flatten_needs(call.cache, need_of(self.blocks[call.layer])).items():
+                    if needs.get(cid) != need:
+                        raise ValueError(f"layer {call.layer} reads cache {call.cache}, whose owner stores something else")
         return needs
 
     def all_parts(self) -> List[object]:

@@ -1478,7 +1478,7 @@ class CudaKernels:
         return {"n_split": self.attention_splits(num_seqs, num_kv_heads, min(max_ctx, chunk or window or max_ctx))}
 
     def _chunked_attention_mma(self, qp, ld_q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, chunk, window, r1, r2, gp, ld_g,
-                               n, n_split) -> None:
+                               n, n_split, sink=None) -> None:
         if k_cache.shape[1] != nkv or k_cache.shape[3] != hd or v_cache.shape != k_cache.shape:
             raise KernelError("chunked_attention: cache shapes do not match the head counts")
         bt = meta.block_table
@@ -1495,8 +1495,8 @@ class CudaKernels:
             _check(fn(qp, ld_q, _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"), _cuda(out, "attention out"),
                       _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                       _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, nh, nkv, hd,
-                      k_cache.shape[2], k_cache.shape[0], scale, window or 0, chunk or 0, status.data_ptr(), None,
-                      _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g, _stream()), "chunked attention (tcgen05)")
+                      k_cache.shape[2], k_cache.shape[0], scale, window or 0, chunk or 0, status.data_ptr(),
+                      _cuda(sink, "sink", torch.float32), _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g, _stream()), "chunked attention (tcgen05)")
             return
         if self._stages_set != self.DECODE_STAGES:
             self.set_decode_stages(self.DECODE_STAGES)
@@ -1522,8 +1522,189 @@ class CudaKernels:
                   part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                   _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, nh, nkv, hd,
                   k_cache.shape[2], k_cache.shape[0], scale, window or 0, chunk or 0, n_split,
-                  (2 if cluster else 1) if small else 0, self._decode_status(out.device) if small else None, None,
-                  _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g, _stream()), "chunked attention (mma)")
+                  (2 if cluster else 1) if small else 0, self._decode_status(out.device) if small else None,
+                  _cuda(sink, "sink", torch.float32), _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g,
+                  _stream()), "chunked attention (mma)")
+
+    # ---- a sub-layer output that passes a norm of its own before it joins the stream (csrc/residual_ops.cu) -----------------
+    def normed_add_rms_norm(self, residual: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor],
+                            post_eps: float, extra: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                            out: Optional[torch.Tensor]) -> None:
+        """``residual += y / sqrt(mean(y^2) + post_eps) * post_weight`` (``y`` as it is without ``post_weight``) ``+ extra``
+        (float32 rows), all in float32 and in place; ``out`` (optional) receives ``residual / sqrt(mean(residual^2) + eps) *
+        weight``.  Each of ``y``, ``extra``, ``out`` may be None."""
+        n, h = residual.shape
+        act = out if out is not None else y
+        if act is None:
+            if extra is None:
+                return
+            act = residual
+        for name, t in (("y", y), ("out", out)):
+            if t is not None and (t.shape != residual.shape or t.dtype != act.dtype):
+                raise KernelError(f"normed_add_rms_norm: {name} {tuple(t.shape)} {t.dtype} does not match the stream {tuple(residual.shape)}")
+        if extra is not None and (extra.shape != residual.shape or extra.dtype != torch.float32):
+            raise KernelError("normed_add_rms_norm: the second addend must be float32 rows of the stream's shape")
+        if (out is not None and (weight is None or weight.numel() != h)) or (post_weight is not None and post_weight.numel() != h):
+            raise KernelError("normed_add_rms_norm: a norm's weight does not match the stream")
+        fn = _fn("residual_ops", "iian_normed_add_rms_norm",
+                 [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+        _check(fn(_cuda(residual, "residual", torch.float32), _cuda(y, "addend"), _cuda(post_weight, "addend norm weight", torch.float32),
+                  post_eps, _cuda(extra, "second addend", torch.float32), _cuda(weight, "norm weight", torch.float32),
+                  _cuda(out, "norm out"), _code(act, "norm out"), n, h, eps, _stream()), "normed_add_rms_norm")
+
+    def weighted_sum2(self, x: torch.Tensor, a: float, y: torch.Tensor, b: float, out: torch.Tensor) -> None:
+        """``out = a x + b y`` element by element (one dtype, one shape)."""
+        if x.shape != y.shape or out.shape != x.shape or x.dtype != y.dtype or out.dtype != x.dtype:
+            raise KernelError("weighted_sum2: x, y and out must share shape and dtype")
+        fn = _fn("stream_ops", "iian_weighted_sum2", [c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_longlong, c_void_p])
+        _check(fn(_cuda(x, "x"), a, _cuda(y, "y"), b, _cuda(out, "out"), _code(x, "x"), x.numel(), _stream()), "weighted_sum2")
+
+    def head_norm_gate_act(self, x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, *,
+                           num_heads: int, eps: float, gate_act: str = "sigmoid") -> None:
+        """``head_norm_gate`` with the gate's column passing ``gate_act`` (``sigmoid`` | ``silu``) before it multiplies."""
+        n, m = x.shape
+        if m % num_heads or weight.numel() != m or out.shape != (n, m) or (gate is not None and (gate.shape != (n, m) or gate.dtype != out.dtype)):
+            raise KernelError("head_norm_gate_act: shapes or dtypes do not fit")
+        gp, ld = self._rows(gate, "gate")
+        fn = _fn("stream_ops", "iian_head_norm_gate_act", [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int,
+                                                           c_float, c_int, c_void_p])
+        _check(fn(_cuda(x, "heads", torch.float32), _cuda(weight, "head norm weight", torch.float32), gp, ld, _cuda(out, "head norm out"),
+                  _code(out, "head norm out"), n, num_heads, m // num_heads, eps, {"sigmoid": 0, "silu": 1}[gate_act], _stream()),
+               "head_norm_gate_act")
+
+    # ---- rotated attention with a window that keeps the first keys, a sink and a gate per head (csrc/window_attention.cu) ---
+    def rotary_table_scaled(self, inv_freq64: torch.Tensor, positions: torch.Tensor, half: int, magnitude: float, out: torch.Tensor) -> None:
+        """cos and sin of ``position * inv_freq64`` (product and functions in float64) times ``magnitude`` -> float32 [N, half, 2]."""
+        n = positions.shape[0]
+        if inv_freq64.dtype != torch.float64 or inv_freq64.numel() < half or out.shape != (n, half, 2) or out.dtype != torch.float32:
+            raise KernelError("rotary_table_scaled: frequencies float64 [half], out float32 [N, half, 2]")
+        fn = _fn("window_attention", "iian_rotary_table_scaled", [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_double, c_void_p])
+        _check(fn(_cuda(inv_freq64, "frequencies"), _cuda(positions, "positions", torch.int32), _cuda(out, "rotary table"), n, half,
+                  magnitude, _stream()), "rotary_table_scaled")
+
+    def rotate_unit_store(self, proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor,
+                          k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], table: Optional[torch.Tensor],
+                          slots: Optional[torch.Tensor], *, num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, rot_dim: int,
+                          eps: float, unit_norm: bool) -> None:
+        """Per token: rotate the first ``rot_dim`` entries of every head of q and k (entry i with i + rot_dim / 2, angles from
+        ``table``), then divide each head by its root mean square (``unit_norm``); q to ``q_out`` [N, heads, k_dim], k and the
+        values as projected to the token's cache cells (``k_cache`` None: q only)."""
+        n = proj.shape[0]
+        pp, ld = self._rows(proj, "projections")
+        if q_out.shape != (n, num_heads, k_dim) or q_out.dtype != proj.dtype:
+            raise KernelError("rotate_unit_store: q_out must be [N, heads, k_dim] in the projections' dtype")
+        if k_cache is not None and (k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != k_dim or v_cache.shape[3] != v_dim
+                                    or k_cache.shape[:3] != v_cache.shape[:3] or k_cache.dtype != proj.dtype or slots.numel() != n):
+            raise KernelError(f"rotate_unit_store: caches {tuple(k_cache.shape)} / {tuple(v_cache.shape)} do not fit")
+        if rot_dim and (table is None or table.shape != (n, rot_dim // 2, 2) or table.dtype != torch.float32):
+            raise KernelError("rotate_unit_store: the rotation table must be float32 [N, rot_dim / 2, 2]")
+        fn = _fn("window_attention", "iian_rotate_unit_store",
+                 [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                  c_int, c_int, c_int, c_int, c_longlong, c_float, c_int, c_void_p])
+        page = k_cache.shape[2] if k_cache is not None else 1
+        cells = k_cache.shape[0] * k_cache.shape[2] if k_cache is not None else 0
+        _check(fn(pp, ld, q_off, k_off, v_off, _cuda(q_out, "queries"), _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"),
+                  _cuda(table if rot_dim else None, "rotary table"), _cuda(slots, "slots", torch.int32), _code(proj, "projections"), n,
+                  num_heads, num_kv_heads if k_cache is not None else 0, k_dim, v_dim, rot_dim, page, cells, eps, 1 if unit_norm else 0,
+                  _stream()), "rotate_unit_store")
+
+    WINDOW_ATTENTION_MMA = os.environ.get("IIAN_WINDOW_ATTENTION_MMA", "1") not in ("0", "false", "off")
+
+    def window_attention_mma_ok(self, dtype, num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float,
+                                keep_first: int) -> bool:
+        """Whether the tensor-core kernels of ``csrc/attention_mma.cu`` / ``attention_tc.cu`` serve this attention."""
+        return (self.WINDOW_ATTENTION_MMA and not keep_first
+                and self.chunked_attention_mma_ok(dtype, num_heads, num_kv_heads, k_dim, v_dim, scale))
+
+    def window_attention_plan(self, num_seqs: int, num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float,
+                              max_ctx: int, window: Optional[int], keep_first: int, dtype: torch.dtype):
+        if not self.window_attention_mma_ok(dtype, num_heads, num_kv_heads, k_dim, v_dim, scale, keep_first):
+            return None
+        return {"n_split": self.attention_splits(num_seqs, num_kv_heads, min(max_ctx, window or max_ctx))}
+
+    def window_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, meta, *,
+                         num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float, window: Optional[int],
+                         keep_first: int, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], gate_per_head: bool,
+                         n_split: Optional[int] = None) -> None:
+        """``q`` [N, heads * k_dim] -> ``out`` [N, heads * v_dim]: softmax of ``q . k * scale`` over the keys ``j <= i`` with
+        ``i - j < window`` or ``j < keep_first``, the denominator also holding ``exp(sink_h)`` if given; weighted sum of the
+        cached values, times ``sigmoid(gate)``: one number per head (``gate_per_head``: rows of ``heads`` numbers) or per entry
+        (rows of ``heads * v_dim``); the gate may be a column slice."""
+        n = q.shape[0]
+        qp, ld_q = self._rows(q, "queries")
+        gp, ld_g = self._rows(gate, "gate")
+        if q.shape[1] != num_heads * k_dim or out.shape != (n, num_heads * v_dim) or out.dtype != q.dtype or k_cache.dtype != q.dtype \
+                or (sink is not None and sink.numel() != num_heads) \
+                or (gate is not None and (gate.shape != (n, num_heads if gate_per_head else num_heads * v_dim) or gate.dtype != q.dtype)):
+            raise KernelError(f"window_attention: q {tuple(q.shape)}, out {tuple(out.shape)} do not fit")
+        if self.window_attention_mma_ok(q.dtype, num_heads, num_kv_heads, k_dim, v_dim, scale, keep_first) and ld_q % 8 == 0 \
+                and qp % 16 == 0 and (gate is None or gate_per_head or (ld_g % 2 == 0 and gp % 4 == 0)):
+            elementwise = gate is not None and not gate_per_head
+            self._chunked_attention_mma(qp, ld_q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, k_dim, scale, None, window,
+                                        None, None, gp if elementwise else 0, ld_g if elementwise else 0, n, n_split, sink=sink)
+            if gate is not None and gate_per_head:
+                fn = _fn("window_attention", "iian_head_gate", [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
+                _check(fn(_cuda(out, "attention out"), gp, ld_g, _code(out, "attention out"), n, num_heads, v_dim, _stream()), "head_gate")
+            return
+        bt = meta.block_table
+        fn = _fn("window_attention", "iian_window_attention",
+                 [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                  c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+        _check(fn(qp, ld_q, _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"), _cuda(out, "attention out"),
+                  _cuda(meta.positions, "positions", torch.int32), _cuda(meta.seq_of_token, "seq_of_token", torch.int32),
+                  _cuda(bt, "block table", torch.int32), bt.shape[1], _cuda(meta.ctx_len, "ctx_len", torch.int32), _code(q, "queries"),
+                  n, num_heads, num_kv_heads, k_dim, v_dim, k_cache.shape[2], k_cache.shape[0], scale, window or 0, keep_first,
+                  _cuda(sink, "sink", torch.float32), gp, ld_g, 1 if gate_per_head else 0, _stream()), "window_attention")
+
+    # ---- linear attention with a decay: a matrix state per head (csrc/decay_scan.cu) -----------------------------------------
+    def decay_scan(self, proj: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, cu_q: torch.Tensor,
+                   state_slots: torch.Tensor, out: torch.Tensor, *, num_heads: int, dim: int, v_dim: int, activation: Optional[str],
+                   q_scale: float, head_decay: Optional[torch.Tensor] = None, z: Optional[torch.Tensor] = None,
+                   z_bias: Optional[torch.Tensor] = None, tau: float = 1.0, max_q_len: int = 0) -> None:
+        """Walk every sequence's tokens of this step through ``S <- diag(a) S + k v^T``, ``o = S^T q`` from and into ``state``
+        [slots, heads, dim, v_dim] (float32).  ``proj`` rows hold q, k, v at the given column offsets (``activation`` ``silu``:
+        all three pass it first); q is multiplied by ``q_scale``.  The decay is ``head_decay`` [heads] (one constant per head)
+        or, per token and key channel, ``sigmoid(z + z_bias)^(1 / tau)`` with ``z`` float32 [N, heads * dim] (may be a column
+        slice).  ``out`` float32 [N, heads * v_dim]."""
+        n = proj.shape[0]
+        pp, ld = self._rows(proj, "projections")
+        zp, ld_z = self._rows(z, "decay pre-activations")
+        s = cu_q.numel() - 1
+        if out.shape != (n, num_heads * v_dim) or state_slots.numel() != s or state.dim() != 4 or state.shape[1:] != (num_heads, dim, v_dim) \
+                or (head_decay is None) == (z is None) or (head_decay is not None and head_decay.numel() != num_heads) \
+                or (z is not None and (z.shape != (n, num_heads * dim) or z.dtype != torch.float32)) \
+                or (z_bias is not None and z_bias.numel() != num_heads * dim) or activation not in (None, "silu"):
+            raise KernelError("decay_scan: shapes do not fit")
+        fn = _fn("decay_scan", "iian_decay_scan",
+                 [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_void_p,
+                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(pp, ld, q_off, k_off, v_off, 1 if activation == "silu" else 0, q_scale, _cuda(head_decay, "head decays", torch.float32),
+                  zp, ld_z, _cuda(z_bias, "decay bias", torch.float32), 1.0 / tau, _cuda(state, "state", torch.float32),
+                  _cuda(cu_q, "cu_q", torch.int32), _cuda(state_slots, "state slots", torch.int32), _cuda(out, "scan out", torch.float32),
+                  _code(proj, "projections"), s, num_heads, dim, v_dim, state.shape[0], max_q_len, _stream()), "decay_scan")
+
+    # ---- experts weighed by the softmax over the chosen logits; an addend in the experts' sum (csrc/moe.cu) ------------------
+    def moe_route_softmax(self, logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+        """Router logits (float32, may be a column slice) plus ``bias`` -> the ``top`` experts with the largest values (ties to
+        the lower index) and the softmax over those values alone."""
+        n, e = logits.shape
+        if logits.dtype != torch.float32 or ids.shape != (n, top) or weights.shape != (n, top) or (bias is not None and bias.numel() != e):
+            raise KernelError("moe_route_softmax: logits float32 [N, E]; bias [E]; ids / weights [N, top]")
+        lp, ld = self._rows(logits, "router logits")
+        fn = _fn("moe", "iian_moe_route_softmax", [c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+        _check(fn(lp, ld, _cuda(bias, "router bias", torch.float32), e, top, _cuda(ids, "expert ids", torch.int32),
+                  _cuda(weights, "expert weights", torch.float32), n, _stream()), "moe_route_softmax")
+
+    def moe_combine_add(self, ys: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, top: int, weights: Optional[torch.Tensor],
+                        add: torch.Tensor) -> None:
+        """``out[t] = sum_k weights[t, k] * ys[pos[t, k]] + add[t]`` (k ascending, float32); ``add`` may be ``out`` itself."""
+        n, w = out.shape
+        if ys.shape != (n * top, w) or ys.dtype != out.dtype or add.shape != out.shape or add.dtype != out.dtype \
+                or (weights is not None and weights.numel() != n * top):
+            raise KernelError("moe_combine_add: ys must be [N * top, W] and add [N, W] in the dtype of out")
+        fn = _fn("moe", "iian_moe_combine_add", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(_cuda(ys, "moe out rows"), _cuda(pos, "pos", torch.int32), _cuda(weights, "expert weights", torch.float32),
+                  _cuda(add, "addend"), _cuda(out, "moe out"), _code(out, "moe out"), n, w, top, _stream()), "moe_combine")
 
     # ---- the delta rule with a decay per key channel (csrc/delta_rule.cu) ---------------------------------------------------
     @staticmethod

@@ -109,6 +109,24 @@ def prefix_reusable(need) -> bool:
     return is_paged(need)
 
 
+# A mixer made of several mixers side by side answers ``cache_need()`` with a TUPLE of needs, one per member (None for a
+# member without a cache).  The run order still names ONE cache id per call; member j's cache gets the id
+# ``member_cache_id(cache, j)``, the cache manager and the storage see it as a cache of its own (pages grouped, windowed and
+# freed by its own need; a state slot of its own tensor), and ``CacheStorage.view(cache)`` hands the call a tuple of views.
+MEMBER_STRIDE = 1 << 20
+
+
+def member_cache_id(cache: int, member: int) -> int:
+    return (member + 1) * MEMBER_STRIDE + cache
+
+
+def flatten_needs(cache: int, need) -> Dict[int, object]:
+    """cache id -> need for what a call's ``cache_need()`` answered (a tuple spreads over member ids)."""
+    if isinstance(need, tuple):
+        return {member_cache_id(cache, j): n for j, n in enumerate(need) if n is not None}
+    return {} if need is None else {cache: need}
+
+
 class Part:
     def __init__(self, spec: PartSpec, dtype: torch.dtype, device: torch.device):
         self.spec = spec
@@ -161,6 +179,18 @@ class NormOut:
         partials = ctx.buf(f"norm_partials_{self.name}", (n, k.norm_parts(w, n)), torch.float32)
         k.linear(x, w, out, residual_norm=ResidualNorm(self.residual, self.weight, partials))
         return Prenormed(out, RowScale(partials, width, self.eps), self.norm)
+
+
+@dataclass
+class NormedAddend:
+    """A sub-layer output that still has to pass a norm of its own before it joins the stream: the stream becomes
+    ``x + y / sqrt(mean(y^2) + eps) * weight`` (+ ``extra``, float32 rows, if given).  A block may hand this on as its
+    ``delta``; the norm that runs next does both norms and the sum in one kernel (``ops: normed_add_rms_norm``).
+    ``y`` None: only ``extra`` is owed."""
+    y: Optional[torch.Tensor]
+    weight: Optional[torch.Tensor]
+    eps: float
+    extra: Optional[torch.Tensor] = None
 
 
 class Norm(Part):

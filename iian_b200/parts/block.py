@@ -266,6 +266,67 @@ class ScaledResidualBlock:
         return residual, None
 
 
+@register_block("sandwich_residual")
+class SandwichResidualBlock:
+    """``x += nb1(mixer(n1 x))``; ``x += nb2(ffn(n2 x))``: a norm before AND after each sub-layer.
+
+    Slots: ``mixer_norm``, ``mixer``; optionally ``feed_forward`` with ``feed_forward_norm``; in ``extra``
+    ``mixer_post_norm`` and (with a feed-forward) ``feed_forward_post_norm``, norms that offer ``as_addend`` (``rms_norm``).
+    A sub-layer's output is not added by a kernel of its own: wrapped as a ``NormedAddend`` it goes to the norm that runs
+    next, whose kernel normalises it, adds it to the float32 stream and normalises the stream (the block's last one is handed
+    on as ``delta``).  With ``select_rows`` (the run order's last entry) only the wanted rows go on after the mixer."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        need = ["mixer", "mixer_norm", "mixer_post_norm"]
+        if spec.slot("feed_forward") is not None:
+            need += ["feed_forward_norm", "feed_forward_post_norm"]
+        missing = [s for s in need if spec.slot(s) is None]
+        if missing:
+            raise ValueError(f"arrangement sandwich_residual needs the slots {', '.join(missing)}")
+        self.spec = spec
+        self.dtype = dtype
+        self.mixer_norm = NORMS.build(spec.mixer_norm, dtype, device)
+        self.mixer = MIXERS.build(spec.mixer, dtype, device)
+        self.mixer_post_norm = NORMS.build(spec.slot("mixer_post_norm"), dtype, device)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, dtype, device)
+            self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, dtype, device)
+            self.feed_forward_post_norm = NORMS.build(spec.slot("feed_forward_post_norm"), dtype, device)
+        for norm in (self.mixer_post_norm, self.feed_forward_post_norm):
+            if norm is not None and not hasattr(norm, "as_addend"):
+                raise ValueError("arrangement sandwich_residual needs post-norms that can ride in the next norm's sum (rms_norm)")
+
+    def parts(self):
+        out = [("mixer_norm", self.mixer_norm), ("mixer", self.mixer), ("mixer_post_norm", self.mixer_post_norm)]
+        if self.feed_forward is not None:
+            out += [("feed_forward_norm", self.feed_forward_norm), ("feed_forward", self.feed_forward),
+                    ("feed_forward_post_norm", self.feed_forward_post_norm)]
+        return tuple(out)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, residual: torch.Tensor, delta, ctx, cache, writes_cache: bool, select_rows: Optional[torch.Tensor]):
+        h = self.mixer_norm.forward(residual, delta, ctx)            # residual += what was owed; h = n1(residual)
+        y = self.mixer.forward(h, ctx, cache, writes_cache)
+        gathers = select_rows is not None and not getattr(ctx, "rows_identity", False)
+        if gathers:
+            k = ops.kernels()
+            r = select_rows.shape[0]
+            res_sel = ctx.buf("residual_rows", (r, residual.shape[1]), residual.dtype)
+            y_sel = ctx.buf("mixer_out_rows", (r, y.shape[1]), y.dtype)
+            k.gather_rows(residual, select_rows, res_sel)
+            k.gather_rows(y, select_rows, y_sel)
+            residual, y = res_sel, y_sel
+        owed = self.mixer_post_norm.as_addend(y)
+        if self.feed_forward is None:
+            return residual, owed
+        h2 = self.feed_forward_norm.forward(residual, owed, ctx)
+        z = self.feed_forward.forward(h2, ctx)
+        return residual, self.feed_forward_post_norm.as_addend(z)
+
+
 class SigmoidGate:
     """A gate of a sub-layer's output: ``sigmoid(W h + b)`` per element, ``h`` the sub-layer's input.  params: ``size``.
     The matrix rides as extra rows in the sub-layer's own first product (``stack_rows``); the bias and the sigmoid are

@@ -16,6 +16,11 @@ Two further forms, chosen by parameters.  ``score = "table"``: there is no route
 "clamped_swish"``: ``g = min(Wgate u, limit)``, ``v = clamp(Wup u, -limit, limit)``, the expert's hidden row is
 ``g sigmoid(1.702 g) (v + 1)``.
 
+``score = "softmax_top"``: the router has a bias (``router.b``, float32 sum), the ``top`` experts with the largest biased
+logits are taken and weighed by the softmax over those logits ALONE.  ``shared_intermediate_size``: one more gated
+feed-forward of that width (tensors ``shared.gate / up / down``, same activation) that every token uses; its output is added
+to the experts' sum in the kernel that forms it.
+
 ``stack_rows`` puts further rows that read the same input (a gate of the residual) under the router's, so that one
 product with float32 output serves both.
 """
@@ -53,8 +58,19 @@ class RoutedExperts(FeedForward):
             raise ValueError("routed_experts: the clamped activation needs a positive limit")
         self.score = p.get("score", "sigmoid")
         self.weight_on = p.get("weight_on", "input")
-        if self.score not in ("sigmoid", "table") or self.weight_on not in ("input", "output"):
-            raise ValueError("routed_experts: score is 'sigmoid' or 'table', weight_on 'input' or 'output'")
+        if self.score not in ("sigmoid", "softmax_top", "table") or self.weight_on not in ("input", "output"):
+            raise ValueError("routed_experts: score is 'sigmoid', 'softmax_top' or 'table', weight_on 'input' or 'output'")
+        self.shared_inter = int(p.get("shared_intermediate_size", 0) or 0)
+        self.shared = None
+        if self.shared_inter:
+            if self.activation not in ("silu", "gelu_tanh"):
+                raise ValueError("routed_experts: the shared expert takes silu or gelu_tanh")
+            from ..config.spec import PartSpec
+            from .mlp import GatedMLP
+            self.shared = GatedMLP(PartSpec("gated_mlp", {"hidden_size": self.hidden, "intermediate_size": self.shared_inter,
+                                                          "activation": self.activation,
+                                                          "names": ("shared.gate", "shared.up", "shared.down")}), dtype, device)
+        self.router_bias = None
         self.vocab = int(p["vocab_size"]) if self.score == "table" else 0
         self.needs_tokens = self.score == "table"       # forward wants to know which token each row belongs to
         if not 0 < self.top <= self.experts:
@@ -68,6 +84,10 @@ class RoutedExperts(FeedForward):
             t = {"table": TensorSpec((self.vocab, self.top), kind="int", init=f"distinct_rows:{self.experts}")}
         else:
             t = {"router": TensorSpec((self.experts, self.hidden))}
+            if self.score == "softmax_top":
+                t["router.b"] = TensorSpec((self.experts,))
+        if self.shared is not None:
+            t.update(self.shared.tensors())
         for e in range(self.experts):
             t[f"e{e}.gate"] = TensorSpec((self.inter, self.hidden))
             t[f"e{e}.up"] = TensorSpec((self.inter, self.hidden))
@@ -80,6 +100,10 @@ class RoutedExperts(FeedForward):
         else:
             self._router = tensors["router"]
             self.w_router = self._router.contiguous()
+            if self.score == "softmax_top":
+                self.router_bias = tensors["router.b"].to(torch.float32).contiguous()
+        if self.shared is not None:
+            self.shared.bind({k: t for k, t in tensors.items() if k.startswith("shared.")})
         gate = torch.stack([tensors[f"e{e}.gate"] for e in range(self.experts)])
         up = torch.stack([tensors[f"e{e}.up"] for e in range(self.experts)])
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
@@ -101,6 +125,8 @@ class RoutedExperts(FeedForward):
         self.w_router = torch.cat(ws, dim=0).contiguous()
 
     def kernel_libraries(self):
+        if self.shared is not None:
+            return tuple(set(("moe", "gemm_simt") + tuple(self.shared.kernel_libraries())))
         if self.activation == "clamped_swish" and self.dtype == torch.bfloat16:
             return ("moe", "gemm_simt", "postnorm")      # the activation between the two tcgen05 products
         return ("moe", "gemm_simt")        # in bfloat16 the products' fast forms come with gemm_simt (the grouped tcgen05 one too)
@@ -123,7 +149,10 @@ class RoutedExperts(FeedForward):
         else:
             logits = ctx.buf("router_logits", (n, self.w_router.shape[0]), torch.float32)
             k.linear(x, self.w_router, logits)
-            k.moe_route(logits[:, :E], top, ids, wts)
+            if self.score == "softmax_top":
+                k.moe_route_softmax(logits[:, :E], self.router_bias, top, ids, wts)
+            else:
+                k.moe_route(logits[:, :E], top, ids, wts)
         on_input = self.weight_on == "input"
         on_tc = (self.w_gate_up is not None and hasattr(k, "moe_tcgen05_ok")
                  and k.moe_tcgen05_ok(self.dtype, self.hidden, self.inter, self.activation))
@@ -151,11 +180,15 @@ class RoutedExperts(FeedForward):
             else:
                 k.moe_grouped_gemm(xs, self.w_gate, self.w_up, act, offsets, tiles, self.activation, self.limit)
             k.moe_grouped_gemm(act, self.w_down, None, ys, offsets, tiles)
-        out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
-        if on_input:
-            k.moe_combine(ys, pos, out, top)
+        if self.shared is not None:
+            out = self.shared.forward(x, ctx)                      # lands in "ffn_out"; the experts' sum is added onto it
+            k.moe_combine_add(ys, pos, out, top, None if on_input else wts, out)
         else:
-            k.moe_combine(ys, pos, out, top, wts)
+            out = ctx.buf("ffn_out", (n, self.hidden), self.dtype)
+            if on_input:
+                k.moe_combine(ys, pos, out, top)
+            else:
+                k.moe_combine(ys, pos, out, top, wts)
         if with_extra:
             return out, (logits[:, E:] if self.extra_rows is not None else None)
         return out

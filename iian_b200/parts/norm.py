@@ -12,7 +12,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Norm, register_norm
+from .base import Norm, NormedAddend, register_norm
 
 
 @register_norm("rms_norm")
@@ -21,7 +21,9 @@ class RMSNorm(Norm):
     ``weight_offset + w`` (a weight kept around zero has ``weight_offset`` 1).
 
     ``delta`` may be a pair of tensors (the outputs of two sub-layers that read the same norm): the stream becomes
-    ``x + (d1 + d2)``, summed in float32."""
+    ``x + (d1 + d2)``, summed in float32; or a ``NormedAddend`` (a sub-layer output that passes a norm of its own on its way
+    into the stream): both norms and the sum are one kernel.  ``as_addend(y)`` wraps a sub-layer output for THIS norm to be
+    applied to it on its way into the stream."""
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
@@ -43,10 +45,18 @@ class RMSNorm(Norm):
     def foldable(self):
         return (self.weight, self.eps) if self.weight is not None else None
 
+    def as_addend(self, y: torch.Tensor) -> NormedAddend:
+        return NormedAddend(y, self.weight, self.eps)
+
     def forward(self, residual: torch.Tensor, delta, ctx, delta_scale: float = 1.0) -> torch.Tensor:
         """``delta_scale``: the stream becomes ``x + delta_scale * delta`` (a design that adds its sub-layers' outputs with a
         factor)."""
         out = ctx.buf("normed", residual.shape, self.dtype)
+        if isinstance(delta, NormedAddend):
+            if delta_scale != 1.0:
+                raise ValueError("rms_norm: a normalised addend takes no factor")
+            ops.kernels().normed_add_rms_norm(residual, delta.y, delta.weight, delta.eps, delta.extra, self.weight, self.eps, out)
+            return out
         if delta_scale != 1.0 and delta is not None:
             if isinstance(delta, tuple):
                 raise ValueError("rms_norm: a pair of addends takes no factor")

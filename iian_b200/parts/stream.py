@@ -1,5 +1,8 @@
 """Parts that work on the whole residual stream between two layers (``LayerCall.before``).
 
+``add_embedding``: ``x <- x + e`` with ``e`` what the embedding left.  Nothing is launched for it where the block before left
+a ``NormedAddend``: ``e`` rides as the second addend of the sum the next norm does anyway.
+
 ``reinject_embedding``: ``x <- W [x ; e]`` with ``e`` what the embedding left and ``W`` [hidden, 2 hidden] (the columns
 that meet ``x`` first).  A model that runs a stretch of its layers several times puts it before the first layer of every
 run, so that each run sees the input again.  The sum that is still owed to the stream (``delta``) is added while the
@@ -14,7 +17,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import StreamPart, register_stream_part
+from .base import NormedAddend, StreamPart, register_stream_part
 
 
 @register_stream_part("reinject_embedding")
@@ -50,3 +53,21 @@ class EmbeddingReinjection(StreamPart):
         out = ctx.buf(f"reinjected{turn % 2}", (n, self.hidden), torch.float32)
         k.linear(both, self.weight, out)
         return out, None
+
+
+@register_stream_part("add_embedding")
+class EmbeddingAddition(StreamPart):
+    """``x <- x + e``, in float32.  No tensors, no parameters."""
+
+    needs_embedding_out = True
+
+    def kernel_libraries(self):
+        return ("residual_ops",)
+
+    def forward(self, residual: torch.Tensor, delta, ctx):
+        e = ctx.step_cache["embedding_out"]
+        if delta is None:
+            return residual, NormedAddend(None, None, 0.0, extra=e)
+        if isinstance(delta, NormedAddend) and delta.extra is None:
+            return residual, NormedAddend(delta.y, delta.weight, delta.eps, extra=e)
+        raise ValueError("add_embedding: the block before must leave nothing or one normalised addend to the stream")

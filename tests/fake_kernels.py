@@ -430,6 +430,133 @@ class FakeKernels:
             o = o * torch.sigmoid(gate.float())
         out.copy_(o.to(out.dtype))
 
+    # ---- a normalised addend; two mixers side by side; heads' norm with a choice of gate ------------------------
+    def normed_add_rms_norm(self, residual, y, post_weight, post_eps, extra, weight, eps, out):
+        if y is not None:
+            v = y.float()
+            if post_weight is not None:
+                v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + post_eps) * post_weight
+            residual.add_(v)
+        if extra is not None:
+            residual.add_(extra)
+        if out is not None:
+            x = residual
+            out.copy_((x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * weight).to(out.dtype))
+
+    def weighted_sum2(self, x, a, y, b, out):
+        out.copy_((a * x.float() + b * y.float()).to(out.dtype))
+
+    def head_norm_gate_act(self, x, weight, gate, out, *, num_heads, eps, gate_act="sigmoid"):
+        n, m = x.shape
+        v = x.view(n, num_heads, m // num_heads)
+        v = (v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps)).reshape(n, m) * weight
+        if gate is not None:
+            g = gate.float()
+            v = v * (torch.sigmoid(g) if gate_act == "sigmoid" else g * torch.sigmoid(g))
+        out.copy_(v.to(out.dtype))
+
+    # ---- rotated attention with kept first keys, a sink and a gate per head -------------------------------------
+    def rotary_table_scaled(self, inv_freq64, positions, half, magnitude, out):
+        th = positions.double()[:, None] * inv_freq64.double()[None, :half]
+        out[..., 0] = (torch.cos(th) * magnitude).float()
+        out[..., 1] = (torch.sin(th) * magnitude).float()
+
+    def rotate_unit_store(self, proj, q_off, k_off, v_off, q_out, k_cache, v_cache, table, slots, *, num_heads, num_kv_heads,
+                          k_dim, v_dim, rot_dim, eps, unit_norm):
+        n = proj.shape[0]
+        half = rot_dim // 2
+
+        def turn(t):
+            t = t.float().clone()
+            if rot_dim:
+                cos, sin = table[:, None, :, 0], table[:, None, :, 1]
+                a, b = t[..., :half].clone(), t[..., half:rot_dim].clone()
+                t[..., :half] = a * cos - b * sin
+                t[..., half:rot_dim] = a * sin + b * cos
+            if unit_norm:
+                t = t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps)
+            return t
+
+        q_out.copy_(turn(proj[:, q_off:q_off + num_heads * k_dim].reshape(n, num_heads, k_dim)).to(q_out.dtype))
+        if k_cache is None:
+            return
+        k = turn(proj[:, k_off:k_off + num_kv_heads * k_dim].reshape(n, num_kv_heads, k_dim))
+        v = proj[:, v_off:v_off + num_kv_heads * v_dim].reshape(n, num_kv_heads, v_dim)
+        ps = k_cache.shape[2]
+        for t in range(n):
+            s = int(slots[t])
+            if s < 0:
+                continue
+            k_cache[s // ps, :, s % ps, :] = k[t].to(k_cache.dtype)
+            v_cache[s // ps, :, s % ps, :] = v[t].to(v_cache.dtype)
+
+    def window_attention(self, q, k_cache, v_cache, out, meta, *, num_heads, num_kv_heads, k_dim, v_dim, scale, window, keep_first,
+                         sink, gate, gate_per_head, n_split=None):
+        n = q.shape[0]
+        ps = k_cache.shape[2]
+        rep = num_heads // num_kv_heads
+        qf = q.float().reshape(n, num_heads, k_dim)
+        o = torch.zeros(n, num_heads, v_dim)
+        for t in range(n):
+            s = int(meta.seq_of_token[t])
+            if s < 0:
+                continue
+            p = int(meta.positions[t])
+            lo = max(0, p - window + 1) if window else 0
+            js = torch.cat([torch.arange(0, min(keep_first, lo)), torch.arange(lo, p + 1)])
+            pages = meta.block_table[s, (js // ps).long()].long()
+            assert (pages >= 0).all(), "attention reads a page that was given back"
+            kk = k_cache[pages, :, (js % ps).long(), :].float()
+            vv = v_cache[pages, :, (js % ps).long(), :].float()
+            for h in range(num_heads):
+                sc = (kk[:, h // rep, :] @ qf[t, h]) * scale
+                if sink is not None:
+                    sc = torch.cat([sc, sink[h:h + 1]])
+                o[t, h] = torch.softmax(sc, dim=0)[: js.numel()] @ vv[:, h // rep, :]
+        if gate is not None and gate_per_head:
+            o = o * torch.sigmoid(gate.float())[:, :, None]
+        o = o.view(n, num_heads * v_dim)
+        if gate is not None and not gate_per_head:
+            o = o * torch.sigmoid(gate.float())
+        out.copy_(o.to(out.dtype))
+
+    # ---- linear attention with a decay ----------------------------------------------------------------------------
+    def decay_scan(self, proj, q_off, k_off, v_off, state, cu_q, state_slots, out, *, num_heads, dim, v_dim, activation, q_scale,
+                   head_decay=None, z=None, z_bias=None, tau=1.0, max_q_len=0):
+        H, D, V = num_heads, dim, v_dim
+        act = (lambda t: t * torch.sigmoid(t)) if activation == "silu" else (lambda t: t)
+        for s in range(state_slots.numel()):
+            t0, t1, slot = int(cu_q[s]), int(cu_q[s + 1]), int(state_slots[s])
+            if slot < 0:
+                out[t0:t1] = 0
+                continue
+            S = state[slot].clone()
+            for t in range(t0, t1):
+                q = act(proj[t, q_off:q_off + H * D].float()).view(H, D) * q_scale
+                k = act(proj[t, k_off:k_off + H * D].float()).view(H, D)
+                v = act(proj[t, v_off:v_off + H * V].float()).view(H, V)
+                if head_decay is not None:
+                    a = head_decay.float()[:, None].expand(H, D)
+                else:
+                    zz = z[t].float() + (z_bias if z_bias is not None else 0.0)
+                    a = torch.exp(torch.nn.functional.logsigmoid(zz) / tau).view(H, D)
+                S = a[:, :, None] * S + k[:, :, None] * v[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(H * V)
+            state[slot] = S
+
+    def moe_route_softmax(self, logits, bias, top, ids, weights):
+        z = logits.float() + (bias if bias is not None else 0.0)
+        vals, idx = torch.sort(z, dim=-1, descending=True, stable=True)
+        ids.copy_(idx[:, :top].to(torch.int32))
+        weights.copy_(torch.softmax(vals[:, :top], dim=-1))
+
+    def moe_combine_add(self, ys, pos, out, top, weights, add):
+        n = out.shape[0]
+        rows = ys[pos.long()].float().view(n, top, -1)
+        if weights is not None:
+            rows = rows * weights.view(n, top, 1)
+        out.copy_((rows.sum(1) + add.float()).to(out.dtype))
+
     # ---- the delta rule with a decay per key channel --------------------------------------------------------
     def delta_rule(self, proj, col_off, b_off, z, taps, a_log, dt_bias, state, ctx, out, *, num_heads, num_kv_heads, dim, v_dim):
         H, G, D, V = num_heads, num_kv_heads, dim, v_dim
