@@ -252,10 +252,18 @@ def gated_expert(h: torch.Tensor, w: Mapping[str, torch.Tensor], pre: str) -> to
     return mm(silu(mm(h, w[pre + "gate"])) * mm(h, w[pre + "up"]), w[pre + "down"])
 
 
+# A test that wants to know where a router's choice hangs on a hair sets this to a list; every call then appends, per token,
+# the gap between the last chosen logit and the best one left out (infinity where every expert is chosen).
+router_margins: Optional[list] = None
+
+
 def router_choice(h: torch.Tensor, w: Mapping[str, torch.Tensor], pre: str, top: int):
     """``(ids [T, top], weights [T, top])``: the largest logits, softmax over the chosen ones only."""
     z = h @ w[pre + "router"].to(h.dtype).T + w[pre + "router.b"].to(h.dtype)
     vals, ids = torch.topk(z, top, dim=-1)
+    if router_margins is not None:
+        rest = torch.topk(z, top + 1, dim=-1).values[:, top] if top < z.shape[-1] else torch.full_like(vals[:, 0], -math.inf)
+        router_margins.append(vals[:, top - 1] - rest)
     return ids, torch.softmax(vals, dim=-1)
 
 
