@@ -64,16 +64,26 @@ struct AttnParams {
     // the output times sigmoid(gate): rows of nh * HD with ld_gate elements between them; null: none
     const __nv_bfloat16 * gate = nullptr;
     long long ld_gate = 0;
+    // with a window: the first keep_first keys of the sequence stay visible behind it.  The tiles that hold them come first
+    // in a CTA's walk over the keys (a virtual tile number below the window's first tile stands for one of them)
+    int keep_first = 0;
+    // one gate number per head instead of one per entry (rows of nh numbers): the head's size here, 0 otherwise
+    int gate_per_head = 0;
 };
 
 // first key of the chunk that position `pos` lies in
 __device__ __forceinline__ int chunk_start(int pos, int chunk) { return chunk > 0 ? pos - pos % chunk : 0; }
 // the gate's factor for two neighbouring output columns of row (token, head): sigmoid in float32
 __device__ __forceinline__ float2 gate_pair(const AttnParams & p, size_t token, int col) {
+    if (p.gate_per_head) {         // one number per head: gate_per_head holds the head's size
+        const float v = 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[token * p.ld_gate + col / p.gate_per_head])));
+        return make_float2(v, v);
+    }
     const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p.gate + token * p.ld_gate + col));
     return make_float2(1.0f / (1.0f + __expf(-g.x)), 1.0f / (1.0f + __expf(-g.y)));
 }
 __device__ __forceinline__ float gate_one(const AttnParams & p, size_t token, int col) {
+    if (p.gate_per_head) col /= p.gate_per_head;
     return 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[token * p.ld_gate + col])));
 }
 
@@ -182,9 +192,14 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
     const int k_hi = pos0 + tok_max;
     const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : chunk_start(pos0 + tok_min, p.chunk);
     const int tile_lo = k_lo / BN, tile_hi = k_hi / BN;
-    const int n_tiles = tile_hi - tile_lo + 1;
+    // kept first keys: their tiles (those wholly before the window's first tile) are walked first, as virtual tiles
+    // vlo .. tile_lo - 1; phys() gives the tile of the cache a virtual tile stands for
+    const int n_keep = (p.keep_first > 0 && p.window > 0) ? min((p.keep_first + BN - 1) / BN, tile_lo) : 0;
+    const int vlo = tile_lo - n_keep;
+    auto phys = [&](int v) { return v >= tile_lo ? v : v - vlo; };
+    const int n_tiles = tile_hi - vlo + 1;
     const int per = (n_tiles + p.n_split - 1) / p.n_split;
-    const int tile_begin = tile_lo + split * per;
+    const int tile_begin = vlo + split * per;
     const int tile_end = min(tile_hi + 1, tile_begin + per);
 
     const int * bt = p.block_table + (size_t) s * p.max_blocks;
@@ -205,7 +220,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
     // request covers whole contiguous rows.
     auto lookup_rows = [&](int tile, int slot) {
         if (tid < BN) {
-            const int j = tile * BN + tid;
+            const int j = phys(tile) * BN + tid;
             long long cell = -1;
             if (tile < tile_end && j <= k_hi) {
                 const int page = bt[j / p.page_size];
@@ -316,7 +331,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
                 }
             }
             // ---- mask (only on tiles that touch a row's causal or window edge), online softmax ----
-            const int key0 = tile * BN;
+            const int key0 = phys(tile) * BN;
             if (p.pen1 != nullptr) {                        // the distance penalty, in units of raw scores
 #pragma unroll
                 for (int nt = 0; nt < BN / 8; nt++) {
@@ -337,7 +352,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
                     for (int e = 0; e < 4; e++) {
                         const int h = e >> 1;
                         const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window) && j >= row_lo[h];
+                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window || j < p.keep_first) && j >= row_lo[h];
                         if (!vis) sc[nt][e] = -INFINITY;
                     }
                 }
@@ -500,9 +515,14 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
     const int k_hi = pos0 + tok_max;
     const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1) : chunk_start(pos0 + tok_min, p.chunk);
     const int tile_lo = k_lo / BN, tile_hi = k_hi / BN;
-    const int n_tiles = tile_hi - tile_lo + 1;
+    // kept first keys: their tiles (those wholly before the window's first tile) are walked first, as virtual tiles
+    // vlo .. tile_lo - 1; phys() gives the tile of the cache a virtual tile stands for
+    const int n_keep = (p.keep_first > 0 && p.window > 0) ? min((p.keep_first + BN - 1) / BN, tile_lo) : 0;
+    const int vlo = tile_lo - n_keep;
+    auto phys = [&](int v) { return v >= tile_lo ? v : v - vlo; };
+    const int n_tiles = tile_hi - vlo + 1;
     const int per = (n_tiles + p.n_split - 1) / p.n_split;
-    const int tile_begin = tile_lo + split * per;
+    const int tile_begin = vlo + split * per;
     const int tile_end = min(tile_hi + 1, tile_begin + per);
     const int n_my = max(0, tile_end - tile_begin);
     const int * bt = p.block_table + (size_t) s * p.max_blocks;
@@ -513,7 +533,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
     const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? __ffs(p.page_size) - 1 : -1;
     auto lookup_rows = [&](int tile, int slot) {
         if (tid < BN) {
-            const int j = tile * BN + tid;
+            const int j = phys(tile) * BN + tid;
             long long cell = -1;
             if (tile < tile_end && j <= k_hi) {
                 const int blk = page_shift >= 0 ? j >> page_shift : j / p.page_size;
@@ -549,7 +569,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
     auto tma_page = [&](int tile) -> int {
         int page = p.num_pages;                              // out of range: the box is filled with zeros
         if (ld_lane && tile < tile_end) {
-            const int j0 = tile * BN + ld_pg * p.page_size;
+            const int j0 = phys(tile) * BN + ld_pg * p.page_size;
             if (j0 <= k_hi) {
                 const int pg = bt[page_shift >= 0 ? j0 >> page_shift : j0 / p.page_size];
                 if (pg >= 0 && pg < p.num_pages) page = pg;
@@ -766,7 +786,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
                 mma16816(sc[0], qf[ks], b0, b1);
                 mma16816(sc[1], qf[ks], b2, b3);
             }
-            const int key0 = (tile_begin + i) * BN + warp * 16;
+            const int key0 = phys(tile_begin + i) * BN + warp * 16;
             if (p.pen1 != nullptr) {                        // the distance penalty, in units of raw scores
 #pragma unroll
                 for (int nt = 0; nt < 2; nt++) {
@@ -786,7 +806,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
                     for (int e = 0; e < 4; e++) {
                         const int h = e >> 1;
                         const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window) && j >= row_lo[h];
+                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window || j < p.keep_first) && j >= row_lo[h];
                         if (!vis) sc[nt][e] = -INFINITY;
                     }
                 }
@@ -1220,6 +1240,14 @@ IIAN_API int iian_attention_mma_sink(
                                      n_split, small_tiles, status, sink, nullptr, nullptr, nullptr, 0, stream);
 }
 
+IIAN_API int iian_attention_mma_kept(
+    const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
+    int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, int chunk, int n_split, int small_tiles, int * status, const float * sink,
+    const float * pen1, const float * pen2, const void * gate, long long ld_gate, int keep_first, int gate_per_head,
+    cudaStream_t stream);
+
 // The general entry.  q: rows of nh * hd with ld_q elements between them (a multiple of 8).  chunk > 0 (not together
 // with a window): key j is visible to position i iff j <= i and floor(i / chunk) == floor(j / chunk).  pen1, pen2:
 // f32 [nh] or both null: pen1[h] * ln(1 + pen2[h] * (i - j)) is taken off the scaled score (needs scale > 0).
@@ -1231,12 +1259,28 @@ IIAN_API int iian_attention_mma_masked(
     int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
     float scale, int window, int chunk, int n_split, int small_tiles, int * status, const float * sink,
     const float * pen1, const float * pen2, const void * gate, long long ld_gate, cudaStream_t stream) {
+    return iian_attention_mma_kept(q, ld_q, k_cache, v_cache, out, part_o, part_lse, counters, cu_q, ctx_len, block_table, max_blocks, N, S,
+                                   max_q_len, nh, nkv, hd, page_size, num_pages, scale, window, chunk, n_split, small_tiles, status, sink,
+                                   pen1, pen2, gate, ld_gate, 0, 0, stream);
+}
+
+// The same with the first keep_first keys of a sequence visible behind the window (needs a window), and with the gate as one
+// number per head (gate_per_head: rows of nh bf16, any ld_gate >= nh).
+IIAN_API int iian_attention_mma_kept(
+    const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out, float * part_o, float * part_lse,
+    int * counters, const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+    float scale, int window, int chunk, int n_split, int small_tiles, int * status, const float * sink,
+    const float * pen1, const float * pen2, const void * gate, long long ld_gate, int keep_first, int gate_per_head,
+    cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return IIAN_ERR_SHAPE;
     if (sink != nullptr && !(scale > 0.0f)) return IIAN_ERR_SHAPE;
     if ((pen1 == nullptr) != (pen2 == nullptr) || (pen1 != nullptr && !(scale > 0.0f))) return IIAN_ERR_SHAPE;
     if (chunk < 0 || (chunk > 0 && window > 0)) return IIAN_ERR_SHAPE;
     if (ld_q < (long long) nh * hd || (ld_q & 7) || ((uintptr_t) q & 15)) return IIAN_ERR_ALIGN;
-    if (gate != nullptr && ((ld_gate & 1) || ((uintptr_t) gate & 3) || ld_gate < (long long) nh * hd)) return IIAN_ERR_ALIGN;
+    if (gate != nullptr && !gate_per_head && ((ld_gate & 1) || ((uintptr_t) gate & 3) || ld_gate < (long long) nh * hd)) return IIAN_ERR_ALIGN;
+    if (gate != nullptr && gate_per_head && ld_gate < nh) return IIAN_ERR_ALIGN;
     if (gate != nullptr && n_split > 1 && !small_tiles) return IIAN_ERR_SHAPE;
     if (nkv <= 0 || nh % nkv != 0 || page_size <= 0 || n_split < 1) return IIAN_ERR_SHAPE;
     if (hd != 64 && hd != 128) return IIAN_ERR_SHAPE;
@@ -1261,6 +1305,8 @@ IIAN_API int iian_attention_mma_masked(
     p.pen1 = pen1; p.pen2 = pen2;
     p.pen_to_raw = pen1 != nullptr ? 1.0f / p.scale_log2 : 0.0f;
     p.gate = (const __nv_bfloat16 *) gate; p.ld_gate = ld_gate;
+    p.keep_first = keep_first;
+    p.gate_per_head = gate != nullptr && gate_per_head ? hd : 0;
     const int max_rows = max_q_len * (nh / nkv);
     int rc;
     if (cluster) rc = hd == 128 ? launch_decode<128, true>(p, S, max_rows, stream) : launch_decode<64, true>(p, S, max_rows, stream);

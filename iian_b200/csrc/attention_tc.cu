@@ -61,6 +61,11 @@ struct TcAttnParams {
     // the output times sigmoid(gate): rows of nh * 128 with ld_gate elements between them; null: none
     const __nv_bfloat16 * gate = nullptr;
     long long ld_gate = 0;
+    // with a window: the first keep_first keys of the sequence stay visible behind it; the tiles that hold them (those wholly
+    // before the window's first tile) are walked first
+    int keep_first = 0;
+    // one gate number per head (rows of nh numbers) instead of one per entry
+    int gate_per_head = 0;
 };
 
 __device__ __forceinline__ unsigned at_smem(const void * p) { return (unsigned) __cvta_generic_to_shared(p); }
@@ -202,8 +207,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1)
                                   : p.chunk > 0 ? (pos0 + tok_min) - (pos0 + tok_min) % p.chunk : 0;
     const int tile_lo = k_lo / AT_BN, tile_hi = k_hi / AT_BN;
-    const int n_tiles = tile_hi - tile_lo + 1;
-    const int n_grp[2] = {k_hi_a / AT_BN - tile_lo + 1, has_b ? n_tiles : 0};
+    const int n_keep = (p.keep_first > 0 && p.window > 0) ? min((p.keep_first + AT_BN - 1) / AT_BN, tile_lo) : 0;
+    auto phys = [&](int i) { return i < n_keep ? i : tile_lo + i - n_keep; };        // the cache tile of the i-th tile walked
+    const int n_tiles = tile_hi - tile_lo + 1 + n_keep;
+    const int n_grp[2] = {k_hi_a / AT_BN - tile_lo + 1 + n_keep, has_b ? n_tiles : 0};
     const int * bt = p.block_table + (size_t) s * p.max_blocks;
     int * status = p.status;
 
@@ -279,7 +286,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
         auto page_of = [&](int i) -> int {
             int page = p.num_pages;                          // out of range: the box is filled with zeros
             if (i < n_tiles && lp < pages_per_tile) {
-                const int j0 = (tile_lo + i) * AT_BN + lp * ps;
+                const int j0 = phys(i) * AT_BN + lp * ps;
                 if (j0 <= k_hi) {
                     const int pg = bt[j0 / ps];
                     if (pg >= 0 && pg < p.num_pages) page = pg;
@@ -391,7 +398,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
         bool failed = false;
         for (int i = 0; i < n_mine; i++) {
             const unsigned ph = (unsigned) i & 1u;
-            const int key0 = (tile_lo + i) * AT_BN;
+            const int key0 = phys(i) * AT_BN;
             if (!at_wait(at_smem(&s_full[g]), ph)) { if (lane == 0) { status[0] = 7; status[1] = i; } failed = true; break; }
             at_fence_after();
             // the whole row of S into registers; tensor memory is then free for the next tile's Q K^T
@@ -401,7 +408,11 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             at_wait_ld();
             // visible keys of this row in this tile: columns [lo, hi]; most tiles lie wholly below the diagonal
             const int hi = row_ok ? min(AT_BN - 1, row_pos - key0) : -1;
-            const int lo = p.window > 0 ? max(0, row_pos - p.window + 1 - key0) : max(0, row_lo - key0);
+            int lo = p.window > 0 ? max(0, row_pos - p.window + 1 - key0) : max(0, row_lo - key0);
+            // kept first keys in this tile: columns [0, kept); where they reach the window's first column the row sees one
+            // stretch from column 0, else two (columns [kept, lo) stay hidden)
+            const int kept = max(0, p.keep_first - key0);
+            if (kept >= lo) lo = 0;
             if (p.pen1 != nullptr) {                // the distance penalty, in units of raw scores (masked keys are set below)
                 const float d0 = (float) (row_pos - key0);
 #pragma unroll
@@ -412,7 +423,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                 if (two_sided) {
 #pragma unroll
                     for (int j = 0; j < AT_BN; j++)
-                        if (j < lo || j > hi) v[j] = 0xff800000u;        // -inf
+                        if ((j < lo && j >= kept) || j > hi) v[j] = 0xff800000u;        // -inf
                 } else {
 #pragma unroll
                     for (int j = 0; j < AT_BN; j++)
@@ -487,14 +498,17 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
         if (n_mine > 0 && !failed) {
             if (at_wait(at_smem(&pv_done[g]), (unsigned) (n_mine - 1) & 1u)) {
                 at_fence_after();
-                const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+                float head_gate = 1.0f;
                 __nv_bfloat16 * dst = nullptr;
                 const __nv_bfloat16 * gsrc = nullptr;
                 if (row_ok) {
                     const int tok = R / G, head = kvh * G + R % G;
                     dst = p.out + ((size_t) (q0 + tok) * p.nh + head) * AT_HD;
-                    if (p.gate != nullptr) gsrc = p.gate + (size_t) (q0 + tok) * p.ld_gate + (size_t) head * AT_HD;
+                    if (p.gate != nullptr && !p.gate_per_head) gsrc = p.gate + (size_t) (q0 + tok) * p.ld_gate + (size_t) head * AT_HD;
+                    if (p.gate != nullptr && p.gate_per_head) head_gate = 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(size_t) (q0 + tok) * p.ld_gate + head])));
                 }
+                inv *= head_gate;
                 unsigned o[AT_HD];                  // the whole row at once: one wait for four loads
 #pragma unroll
                 for (int c0 = 0; c0 < AT_HD; c0 += 32) at_ld32(tO + lane_addr + (unsigned) c0, o + c0);
@@ -605,17 +619,38 @@ IIAN_API int iian_attention_tc_sink(const void * q, const void * k_cache, const 
 // [nh] or both null: pen1[h] * ln(1 + pen2[h] * (i - j)) is taken off the scaled score (needs scale > 0).  gate: rows of
 // nh * 128 bf16 with ld_gate elements between them (a multiple of 8, 16-byte aligned), or null: the output is multiplied
 // by sigmoid(gate).
+IIAN_API int iian_attention_tc_kept(const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out,
+                                    const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+                                    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+                                    float scale, int window, int chunk, int * status, const float * sink, const float * pen1,
+                                    const float * pen2, const void * gate, long long ld_gate, int keep_first, int gate_per_head,
+                                    cudaStream_t stream);
+
 IIAN_API int iian_attention_tc_masked(const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out,
                                       const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
                                       int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
                                       float scale, int window, int chunk, int * status, const float * sink, const float * pen1,
                                       const float * pen2, const void * gate, long long ld_gate, cudaStream_t stream) {
+    return iian_attention_tc_kept(q, ld_q, k_cache, v_cache, out, cu_q, ctx_len, block_table, max_blocks, N, S, max_q_len, nh, nkv, hd,
+                                  page_size, num_pages, scale, window, chunk, status, sink, pen1, pen2, gate, ld_gate, 0, 0, stream);
+}
+
+// The same with the first keep_first keys of a sequence visible behind the window (needs a window), and with the gate as one
+// number per head (gate_per_head: rows of nh bf16, any ld_gate >= nh).
+IIAN_API int iian_attention_tc_kept(const void * q, long long ld_q, const void * k_cache, const void * v_cache, void * out,
+                                    const int * cu_q, const int * ctx_len, const int * block_table, int max_blocks,
+                                    int N, int S, int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+                                    float scale, int window, int chunk, int * status, const float * sink, const float * pen1,
+                                    const float * pen2, const void * gate, long long ld_gate, int keep_first, int gate_per_head,
+                                    cudaStream_t stream) {
     if (N <= 0 || S <= 0) return IIAN_OK;
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) return IIAN_ERR_SHAPE;
     if (sink != nullptr && !(scale > 0.0f)) return IIAN_ERR_SHAPE;
     if ((pen1 == nullptr) != (pen2 == nullptr) || (pen1 != nullptr && !(scale > 0.0f))) return IIAN_ERR_SHAPE;
     if (chunk < 0 || (chunk > 0 && window > 0)) return IIAN_ERR_SHAPE;
     if (ld_q < (long long) nh * hd || (ld_q & 7)) return IIAN_ERR_ALIGN;
-    if (gate != nullptr && ((ld_gate & 7) || ((uintptr_t) gate & 15) || ld_gate < (long long) nh * hd)) return IIAN_ERR_ALIGN;
+    if (gate != nullptr && !gate_per_head && ((ld_gate & 7) || ((uintptr_t) gate & 15) || ld_gate < (long long) nh * hd)) return IIAN_ERR_ALIGN;
+    if (gate != nullptr && gate_per_head && ld_gate < nh) return IIAN_ERR_ALIGN;
     if (hd != AT_HD || nkv <= 0 || nh % nkv != 0) return IIAN_ERR_SHAPE;
     if (page_size != 8 && page_size != 16 && page_size != 32 && page_size != 64 && page_size != 128) return IIAN_ERR_SHAPE;
     if (status == nullptr) return IIAN_ERR_SHAPE;
@@ -638,6 +673,8 @@ IIAN_API int iian_attention_tc_masked(const void * q, long long ld_q, const void
     p.pen1 = pen1; p.pen2 = pen2;
     p.pen_to_raw = pen1 != nullptr ? 1.0f / p.scale_log2 : 0.0f;
     p.gate = (const __nv_bfloat16 *) gate; p.ld_gate = ld_gate;
+    p.keep_first = keep_first;
+    p.gate_per_head = gate != nullptr && gate_per_head ? 1 : 0;
     const size_t smem = (size_t) 6 * AT_TILE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {

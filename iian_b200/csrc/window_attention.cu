@@ -208,20 +208,6 @@ __global__ void window_attention_kernel(
     }
 }
 
-// out[t, h, :] *= sigmoid(gate[t, h]) for outputs another attention kernel wrote without the gate
-template <typename A>
-__global__ void head_gate_kernel(A * __restrict__ out, const A * __restrict__ gate, long long ld_gate, int nh, int dv, long long total) {
-    pdl_wait();
-    pdl_launch_dependents();
-    const long long idx = (long long) blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const long long th = idx / dv;
-    const long long t = th / nh;
-    const int h = (int) (th % nh);
-    const float g = 1.0f / (1.0f + expf(-to_f32(gate[t * ld_gate + h])));
-    out[idx] = from_f32<A>(to_f32(out[idx]) * g);
-}
-
 }  // namespace iian
 
 using namespace iian;
@@ -281,19 +267,5 @@ IIAN_API int iian_window_attention(const void * q, long long ld_q, const void * 
                            (__nv_bfloat16 *) out, positions, seq_of_token, block_table, max_blocks, ctx_len, N, nh, nkv, dk, dv,
                            page_size, num_pages, scale, window, keep_first, sink, (const __nv_bfloat16 *) gate, ld_gate,
                            gate_per_head);
-    return IIAN_ERR_DTYPE;
-}
-
-// out: A [N, nh * dv] in place; gate: rows of nh numbers with row stride ld_gate
-IIAN_API int iian_head_gate(void * out, const void * gate, long long ld_gate, int act_dtype, int N, int nh, int dv,
-                            cudaStream_t stream) {
-    const long long total = (long long) N * nh * dv;
-    if (total <= 0) return IIAN_OK;
-    const unsigned blocks = (unsigned) ((total + 255) / 256);
-    if (act_dtype == IIAN_F32)
-        return iian_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float *) out, (const float *) gate, ld_gate, nh, dv, total);
-    if (act_dtype == IIAN_BF16)
-        return iian_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16 *) out,
-                           (const __nv_bfloat16 *) gate, ld_gate, nh, dv, total);
     return IIAN_ERR_DTYPE;
 }

@@ -1478,25 +1478,26 @@ class CudaKernels:
         return {"n_split": self.attention_splits(num_seqs, num_kv_heads, min(max_ctx, chunk or window or max_ctx))}
 
     def _chunked_attention_mma(self, qp, ld_q, k_cache, v_cache, out, meta, nh, nkv, hd, scale, chunk, window, r1, r2, gp, ld_g,
-                               n, n_split, sink=None) -> None:
+                               n, n_split, sink=None, keep_first: int = 0, gate_per_head: bool = False) -> None:
         if k_cache.shape[1] != nkv or k_cache.shape[3] != hd or v_cache.shape != k_cache.shape:
             raise KernelError("chunked_attention: cache shapes do not match the head counts")
         bt = meta.block_table
         if self.ATTENTION_TC and hd == 128 and k_cache.shape[2] in (8, 16, 32, 64, 128) and ld_q % 8 == 0 \
-                and meta.max_q_len * (nh // nkv) >= self.TC_ATTENTION_MIN_ROWS and gp % 16 == 0 and ld_g % 8 == 0 \
+                and meta.max_q_len * (nh // nkv) >= self.TC_ATTENTION_MIN_ROWS and (gate_per_head or (gp % 16 == 0 and ld_g % 8 == 0)) \
                 and out.data_ptr() % 16 == 0:
             # portions of prompts with heads of 128: tcgen05 (csrc/attention_tc.cu)
             status = self.tcgen05_status_buffer(out.device)
             CudaKernels._tc_used = True
-            fn = _fn("attention_tc", "iian_attention_tc_masked",
+            fn = _fn("attention_tc", "iian_attention_tc_kept",
                      [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                       c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                      c_longlong, c_void_p])
+                      c_longlong, c_int, c_int, c_void_p])
             _check(fn(qp, ld_q, _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"), _cuda(out, "attention out"),
                       _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                       _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, nh, nkv, hd,
                       k_cache.shape[2], k_cache.shape[0], scale, window or 0, chunk or 0, status.data_ptr(),
-                      _cuda(sink, "sink", torch.float32), _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g, _stream()), "chunked attention (tcgen05)")
+                      _cuda(sink, "sink", torch.float32), _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g,
+                      keep_first, 1 if gate_per_head else 0, _stream()), "chunked attention (tcgen05)")
             return
         if self._stages_set != self.DECODE_STAGES:
             self.set_decode_stages(self.DECODE_STAGES)
@@ -1504,7 +1505,7 @@ class CudaKernels:
         if not small:
             n_split = 1
         elif n_split is None:
-            n_split = self.attention_splits(meta.num_seqs, nkv, min(meta.max_ctx, chunk or window or meta.max_ctx))
+            n_split = self.attention_splits(meta.num_seqs, nkv, min(meta.max_ctx, (chunk or window or meta.max_ctx) + keep_first))
         cluster = bool(self.CLUSTER_MERGE and small and n_split in (2, 4, 8, 16))
         part_o = part_lse = counters = 0
         if n_split > 1 and not cluster:
@@ -1514,17 +1515,17 @@ class CudaKernels:
             part_lse = part_o + rows * n_split * hd * 4
             row_tiles = -(-meta.max_q_len * (nh // nkv) // 16)
             counters = self.attention_counters(out.device, meta.num_seqs * nkv * row_tiles).data_ptr()
-        fn = _fn("attention_mma", "iian_attention_mma_masked",
+        fn = _fn("attention_mma", "iian_attention_mma_kept",
                  [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p,
-                  c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p])
+                  c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p])
         _check(fn(qp, ld_q, _cuda(k_cache, "key cache"), _cuda(v_cache, "value cache"), _cuda(out, "attention out"),
                   part_o, part_lse, counters, _cuda(meta.cu_q, "cu_q", torch.int32), _cuda(meta.ctx_len, "ctx_len", torch.int32),
                   _cuda(bt, "block table", torch.int32), bt.shape[1], n, meta.num_seqs, meta.max_q_len, nh, nkv, hd,
                   k_cache.shape[2], k_cache.shape[0], scale, window or 0, chunk or 0, n_split,
                   (2 if cluster else 1) if small else 0, self._decode_status(out.device) if small else None,
                   _cuda(sink, "sink", torch.float32), _cuda(r1, "r1", torch.float32), _cuda(r2, "r2", torch.float32), gp, ld_g,
-                  _stream()), "chunked attention (mma)")
+                  keep_first, 1 if gate_per_head else 0, _stream()), "chunked attention (mma)")
 
     # ---- a sub-layer output that passes a norm of its own before it joins the stream (csrc/residual_ops.cu) -----------------
     def normed_add_rms_norm(self, residual: torch.Tensor, y: Optional[torch.Tensor], post_weight: Optional[torch.Tensor],
@@ -1610,17 +1611,15 @@ class CudaKernels:
 
     WINDOW_ATTENTION_MMA = os.environ.get("IIAN_WINDOW_ATTENTION_MMA", "1") not in ("0", "false", "off")
 
-    def window_attention_mma_ok(self, dtype, num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float,
-                                keep_first: int) -> bool:
+    def window_attention_mma_ok(self, dtype, num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float) -> bool:
         """Whether the tensor-core kernels of ``csrc/attention_mma.cu`` / ``attention_tc.cu`` serve this attention."""
-        return (self.WINDOW_ATTENTION_MMA and not keep_first
-                and self.chunked_attention_mma_ok(dtype, num_heads, num_kv_heads, k_dim, v_dim, scale))
+        return self.WINDOW_ATTENTION_MMA and self.chunked_attention_mma_ok(dtype, num_heads, num_kv_heads, k_dim, v_dim, scale)
 
     def window_attention_plan(self, num_seqs: int, num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float,
                               max_ctx: int, window: Optional[int], keep_first: int, dtype: torch.dtype):
-        if not self.window_attention_mma_ok(dtype, num_heads, num_kv_heads, k_dim, v_dim, scale, keep_first):
+        if not self.window_attention_mma_ok(dtype, num_heads, num_kv_heads, k_dim, v_dim, scale):
             return None
-        return {"n_split": self.attention_splits(num_seqs, num_kv_heads, min(max_ctx, window or max_ctx))}
+        return {"n_split": self.attention_splits(num_seqs, num_kv_heads, min(max_ctx, (window or max_ctx) + keep_first))}
 
     def window_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor, meta, *,
                          num_heads: int, num_kv_heads: int, k_dim: int, v_dim: int, scale: float, window: Optional[int],
@@ -1629,7 +1628,9 @@ class CudaKernels:
         """``q`` [N, heads * k_dim] -> ``out`` [N, heads * v_dim]: softmax of ``q . k * scale`` over the keys ``j <= i`` with
         ``i - j < window`` or ``j < keep_first``, the denominator also holding ``exp(sink_h)`` if given; weighted sum of the
         cached values, times ``sigmoid(gate)``: one number per head (``gate_per_head``: rows of ``heads`` numbers) or per entry
-        (rows of ``heads * v_dim``); the gate may be a column slice."""
+        (rows of ``heads * v_dim``); the gate may be a column slice.  In bfloat16 with keys and values of 64 or 128 entries
+        and a positive scale the tensor-core kernels of ``csrc/attention_mma.cu`` / ``attention_tc.cu`` serve it (kept keys,
+        sink and gate inside them); otherwise the general kernel of ``csrc/window_attention.cu``."""
         n = q.shape[0]
         qp, ld_q = self._rows(q, "queries")
         gp, ld_g = self._rows(gate, "gate")
@@ -1637,14 +1638,11 @@ class CudaKernels:
                 or (sink is not None and sink.numel() != num_heads) \
                 or (gate is not None and (gate.shape != (n, num_heads if gate_per_head else num_heads * v_dim) or gate.dtype != q.dtype)):
             raise KernelError(f"window_attention: q {tuple(q.shape)}, out {tuple(out.shape)} do not fit")
-        if self.window_attention_mma_ok(q.dtype, num_heads, num_kv_heads, k_dim, v_dim, scale, keep_first) and ld_q % 8 == 0 \
+        if self.window_attention_mma_ok(q.dtype, num_heads, num_kv_heads, k_dim, v_dim, scale) and ld_q % 8 == 0 \
                 and qp % 16 == 0 and (gate is None or gate_per_head or (ld_g % 2 == 0 and gp % 4 == 0)):
-            elementwise = gate is not None and not gate_per_head
             self._chunked_attention_mma(qp, ld_q, k_cache, v_cache, out, meta, num_heads, num_kv_heads, k_dim, scale, None, window,
-                                        None, None, gp if elementwise else 0, ld_g if elementwise else 0, n, n_split, sink=sink)
-            if gate is not None and gate_per_head:
-                fn = _fn("window_attention", "iian_head_gate", [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
-                _check(fn(_cuda(out, "attention out"), gp, ld_g, _code(out, "attention out"), n, num_heads, v_dim, _stream()), "head_gate")
+                                        None, None, gp, ld_g, n, n_split, sink=sink, keep_first=keep_first if window else 0,
+                                        gate_per_head=gate is not None and gate_per_head)
             return
         bt = meta.block_table
         fn = _fn("window_attention", "iian_window_attention",

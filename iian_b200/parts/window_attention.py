@@ -99,7 +99,7 @@ class WindowAttention(Mixer):
         return KVNeed(self.nkv, self.hd, keep, self.vd if self.vd != self.hd else None)
 
     def _fast(self) -> bool:
-        return self.dtype == torch.bfloat16 and self.hd == self.vd and self.hd in (64, 128) and self.scale > 0 and not self.keep_first
+        return self.dtype == torch.bfloat16 and self.hd == self.vd and self.hd in (64, 128) and self.scale > 0
 
     def kernel_libraries(self):
         return ("window_attention", "gemm_simt") + (("attention_mma",) if self._fast() else ()) \
