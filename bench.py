@@ -137,7 +137,8 @@ class ClockSampler:
 
 
 def design_arm(args, K: int, W: int) -> int:
-    """``--design galodra | lekilix | senadra``: the design's shapes beside the Qwen3 shapes of equal size (``iian_b200/cli/workloads.py``:
+    """``--design galodra | lekilix | senadra | nogelorn``: the design's shapes beside the Qwen3 shapes of equal size (Nogelorn also
+    beside the Lekilix shapes of equal size) (``iian_b200/cli/workloads.py``:
     ``DESIGN_SHAPES``, ``EQUAL_QWEN3``), decode at batch 1 / 8 / 64 from 1,024-token prompts and prefill of 2,048 tokens,
     device-timed like the default workload; with ``--kernels`` the design's kernels alone beside their like kernels."""
     import torch
@@ -151,7 +152,7 @@ def design_arm(args, K: int, W: int) -> int:
     if args.kernels:
         from iian_b200.cli import design_kernels
         line["kernels"] = {"galodra": design_kernels.run, "lekilix": design_kernels.run_lekilix,
-                           "senadra": design_kernels.run_senadra}[args.design](peaks)
+                           "senadra": design_kernels.run_senadra, "nogelorn": design_kernels.run_nogelorn}[args.design](peaks)
     else:
         names = [n for n in args.design_shapes.split(",") if n] or list(wl.DESIGN_SHAPES[args.design])
         line["shapes"] = wl.design_comparison(names, (1, 8, 64), (PREFILL_TOKENS,), PROMPT_LEN, K, W, peaks,
@@ -175,7 +176,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="the headline and the end-to-end figure only")
     ap.add_argument("--skip-32b", action="store_true", help="leave out the Qwen3-32B shape")
     ap.add_argument("--skip-serve", action="store_true", help="leave out the continuous-batching workload (Qwen3-0.6B shape)")
-    ap.add_argument("--design", default="", choices=["", "galodra", "lekilix", "senadra"],
+    ap.add_argument("--design", default="", choices=["", "galodra", "lekilix", "senadra", "nogelorn"],
                     help="instead of the default workload: decode and prefill throughput of this design at layer sizes of real "
                          "models beside the Qwen3 shape of equal size (one JSON line of its own)")
     ap.add_argument("--design-shapes", default="", help="names of the design's shapes (default: all of them)")

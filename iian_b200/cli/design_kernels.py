@@ -409,6 +409,180 @@ def run_lekilix(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
     return out
 
 
+def run_nogelorn(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
+    """The kernels of the Nogelorn design alone, each beside its like kernel of the Lekilix path at equal size (16 heads of 128
+    on 8 KV heads, window 4,096 with 128 kept first keys; recurrences of 8 heads, 128 deep and 256 wide):
+      decode attention    8 (and 64) sequences of 6,144 cached tokens: window, kept keys, sink, head gate  vs  window and sink
+      prefill attention   one sequence of 2,048 tokens, and of 8,192 (the window passes, the kept keys stay)   flops of scores and values
+      rotation + cache    2,048 tokens: rotation, unit norm, cache write  vs  norm over the projection, rotation, cache write
+      sum + norm          2,048 rows: a normalised addend in the next norm's sum  vs  two plain addends
+      expert products     2,048 (and 8) tokens x 5 of 64 experts by softmax over the chosen logits + a shared one  vs  6 by table
+      decayed scan        8 / 64 sequences of one token (bytes of state) and one sequence of 2,048 tokens, constant decay per
+                          head and decay per channel  vs  the matrix-memory scan
+    """
+    import torch
+    from .. import ops
+    from ..config.spec import PartSpec
+    from ..engine.runner import StepContext, Workspace
+    from ..parts.experts import RoutedExperts
+    from ..parts.matrix_memory import state_block_floats, state_columns
+    k = ops.kernels()
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    nkv, hd, page, window, keep = 8, 128, 16, 4096, 128
+    out = {}
+    hbm, tfl = peaks["hbm_gbs"], peaks["bf16_tflops"]
+
+    def mem_row(name, ms, nbytes):
+        out[name] = {"ms": ms, "gb_s": nbytes / ms / 1e6, "of_hbm_peak": nbytes / ms / 1e6 / hbm}
+
+    def flop_row(name, ms, flops):
+        out[name] = {"ms": ms, "tflops": flops / ms / 1e9, "of_bf16_peak": flops / ms / 1e9 / tfl}
+
+    sink = torch.randn(heads, device=dev)
+    # ---- decode attention: contexts longer than the window, so that the kept keys are a stretch of their own ---------------
+    for B, ctx in ((8, 6144), (64, 6144)):
+        meta, pages = _meta([ctx] * B, [1] * B, page, dev)
+        copies = [(torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3, torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3)
+                  for _ in range(2)]
+        q = torch.randn(B, heads * hd, device=dev).to(bf) * 0.1
+        gate = torch.randn(B, heads, device=dev).to(bf)
+        o = torch.empty(B, heads * hd, device=dev, dtype=bf)
+        ms = _timed([(lambda c=c: k.window_attention(q, c[0], c[1], o, meta, num_heads=heads, num_kv_heads=nkv, k_dim=hd, v_dim=hd,
+                                                     scale=0.088, window=window, keep_first=keep, sink=sink, gate=gate, gate_per_head=True))
+                     for c in copies])
+        mem_row(f"decode_attention_kept_{B}x{ctx}", ms, B * (window + keep) * 2 * nkv * hd * 2)
+        q3 = q.view(B, heads, hd)
+        ms = _timed([(lambda c=c: k.sink_attention(q3, c[0], c[1], o, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088,
+                                                   window=window, sink=sink)) for c in copies])
+        mem_row(f"decode_attention_lekilix_{B}x{ctx}", ms, B * window * 2 * nkv * hd * 2)
+        del copies
+    torch.cuda.empty_cache()
+    # ---- prefill attention -----------------------------------------------------------------------------------------------
+    for T in (2048, 8192):
+        meta, pages = _meta([T], [T], page, dev)
+        kc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+        vc = torch.randn(pages, nkv, page, hd, device=dev).to(bf) * 0.3
+        q = torch.randn(T, heads * hd, device=dev).to(bf) * 0.1
+        gate = torch.randn(T, heads, device=dev).to(bf)
+        o = torch.empty(T, heads * hd, device=dev, dtype=bf)
+        pairs = T * (T + 1) / 2 if T <= window else window * (window + 1) / 2 + (T - window) * window
+        kept_pairs = pairs + (max(0, T - window - keep) * keep if T > window else 0)
+        ms = _timed([lambda: k.window_attention(q, kc, vc, o, meta, num_heads=heads, num_kv_heads=nkv, k_dim=hd, v_dim=hd, scale=0.088,
+                                                window=window, keep_first=keep, sink=sink, gate=gate, gate_per_head=True)] * 3)
+        flop_row(f"prefill_attention_kept_{T}", ms, 4.0 * heads * hd * kept_pairs)
+        q3 = q.view(T, heads, hd)
+        ms = _timed([lambda: k.sink_attention(q3, kc, vc, o, meta, num_heads=heads, num_kv_heads=nkv, head_dim=hd, scale=0.088,
+                                              window=window, sink=sink)] * 3)
+        flop_row(f"prefill_attention_lekilix_{T}", ms, 4.0 * heads * hd * pairs)
+        del kc, vc
+    torch.cuda.empty_cache()
+    # ---- rotation, unit norm, cache write ------------------------------------------------------------------------------------
+    T = 2048
+    meta, pages = _meta([T], [T], page, dev)
+    slots = torch.arange(T, dtype=torch.int32, device=dev)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    wide = (heads + 2 * nkv) * hd
+    sets = [(torch.randn(T, wide, device=dev).to(bf), torch.empty(T, heads, hd, device=dev, dtype=bf),
+             torch.zeros(pages, nkv, page, hd, device=dev, dtype=bf), torch.zeros(pages, nkv, page, hd, device=dev, dtype=bf)) for _ in range(4)]
+    inv64 = torch.pow(torch.tensor(500000.0, dtype=torch.float64), -torch.arange(hd // 2, dtype=torch.float64) / (hd // 2)).to(dev)
+    table = torch.empty(T, hd // 2, 2, device=dev)
+    k.rotary_table_scaled(inv64, pos, hd // 2, 1.0, table)
+    ms = _timed([(lambda t=t: k.rotate_unit_store(t[0], 0, heads * hd, (heads + nkv) * hd, t[1], t[2], t[3], table, slots, num_heads=heads,
+                                                  num_kv_heads=nkv, k_dim=hd, v_dim=hd, rot_dim=hd, eps=1e-6, unit_norm=True)) for t in sets])
+    mem_row("rotate_unit_store", ms, 2 * T * (heads + 2 * nkv) * hd * 2)
+    ms = _timed([lambda: k.rotary_table_scaled(inv64, pos, hd // 2, 1.0, table)] * 4)
+    mem_row("rotary_table_float64_angles", ms, T * hd // 2 * 8)
+    sets2 = [(torch.randn(T, (2 * heads + nkv) * hd, device=dev).to(bf), t[1], t[2], t[3]) for t in sets]
+    qw, kw = torch.ones(heads * hd, device=dev), torch.ones(nkv * hd, device=dev)
+    inv32 = inv64[:32].contiguous()
+    ms = _timed([(lambda t=t: k.projection_norm_rope_store(t[0], 0, heads * hd, t[1], t[2], t[3], num_heads=heads, num_kv_heads=nkv,
+                                                           head_dim=hd, q_weight=qw, k_weight=kw, eps=1e-6, inv_freq=inv32, rot_dim=64,
+                                                           rope_style=1, positions=pos, slots=slots)) for t in sets2])
+    mem_row("projection_norm_rope_store_lekilix", ms, T * (heads + nkv) * hd * 2 + T * (heads + 2 * nkv) * hd * 2)
+    del sets, sets2
+    # ---- sum + norm ------------------------------------------------------------------------------------------------------------
+    n = 2048
+    w = torch.ones(width, device=dev)
+    sets = [(torch.randn(n, width, device=dev), torch.randn(n, width, device=dev).to(bf), torch.randn(n, width, device=dev).to(bf),
+             torch.empty(n, width, device=dev, dtype=bf)) for _ in range(8)]
+    ms = _timed([(lambda t=t: k.normed_add_rms_norm(t[0], t[1], w, 1e-6, None, w, 1e-6, t[3])) for t in sets])
+    mem_row("normed_add_rms_norm", ms, n * width * (4 + 2 + 4 + 2))
+    ms = _timed([(lambda t=t: k.add2_rms_norm(t[0], t[1], t[2], w, 1e-6, t[3])) for t in sets])
+    mem_row("add2_rms_norm_lekilix", ms, n * width * (4 + 2 + 2 + 4 + 2))
+    del sets
+    # ---- expert products: softmax over the chosen logits and a shared expert  vs  experts by table ---------------------------------
+    E, ff, vocab = 64, 1408, 32768
+    parts = {}
+    for name, params in (("softmax", {"top": 5, "activation": "silu", "score": "softmax_top", "shared_intermediate_size": ff}),
+                         ("table_lekilix", {"top": 6, "activation": "clamped_swish", "limit": 7.0, "score": "table", "vocab_size": vocab})):
+        part = RoutedExperts(PartSpec("routed_experts", dict(params, hidden_size=width, num_experts=E, intermediate_size=ff,
+                                                             weight_on="output")), bf, dev)
+        tensors = {}
+        for tn, ts in part.tensors().items():
+            if ts.kind == "int":
+                tensors[tn] = torch.stack([torch.randperm(E)[:6] for _ in range(vocab)]).to(torch.int32).to(dev)
+            else:
+                tensors[tn] = torch.randn(*ts.shape, device=dev).to(bf) * (1.0 if tn.startswith("router") else 0.02)
+        part.bind(tensors)
+        del tensors
+        parts[name] = part
+    for n in (2048, 8):
+        h = torch.randn(n, width, device=dev).to(bf)
+        for name, part in parts.items():
+            ctx_ = StepContext(Workspace(dev))
+            ctx_.tokens = torch.randint(0, vocab, (n,), device=dev).to(torch.int32)
+            part.forward(h, ctx_)
+            ms = _timed(lambda: part.forward(h, ctx_))
+            if n >= 128:
+                flop_row(f"expert_feed_forward_{name}_{n}", ms, 2.0 * n * 6 * 3 * ff * width)
+            else:
+                reached = len(set(ctx_.buf("expert_ids", (n, part.top), torch.int32).flatten().tolist())) + (1 if part.shared is not None else 0)
+                mem_row(f"expert_feed_forward_{name}_{n}", ms, reached * 3 * ff * width * 2)
+    del parts
+    torch.cuda.empty_cache()
+    # ---- the decayed scan beside the matrix-memory scan --------------------------------------------------------------------------------
+    H, d, dv = heads // 2, 128, 256
+    cb = state_columns(d, dv)
+    wide = 2 * H * d + 2 * H * dv
+    decay = torch.linspace(0.6, 0.999, H, device=dev)
+    bias = torch.zeros(2 * H, device=dev)
+    zb = torch.zeros(H * d, device=dev)
+    for B, L in ((8, 1), (64, 1), (1, 2048)):
+        n = B * L
+        cu = torch.arange(0, n + 1, L, dtype=torch.int32, device=dev)
+        sl = torch.arange(B, dtype=torch.int32, device=dev)
+        sets = [(torch.randn(n, wide, device=dev).to(bf) * 0.5, torch.randn(n, H * d, device=dev), torch.zeros(B, H, dv // 16, d, 16, device=dev),
+                 torch.empty(n, H * dv, device=dev)) for _ in range(4 if L == 1 else 1)]
+        for tag, kw in (("head", {"head_decay": decay, "activation": "silu"}), ("channel", {"z_bias": zb, "tau": 16.0, "activation": None})):
+            ms = _timed([(lambda t=t: k.decay_scan(t[0], 0, H * d, 2 * H * d, t[2], cu, sl, t[3], num_heads=H, dim=d, v_dim=dv, q_scale=1.0,
+                                                   max_q_len=L, **(dict(kw, z=t[1]) if tag == "channel" else kw))) for t in sets])
+            if L == 1:
+                mem_row(f"decay_scan_{tag}_decode_{B}", ms, B * 2 * H * d * dv * 4)
+            else:
+                flop_row(f"decay_scan_{tag}_prefill_{L}", ms, 4.0 * L * H * d * dv)
+        del sets
+        sets = [(torch.randn(n, wide, device=dev).to(bf) * 0.5, torch.randn(n, 2 * H, device=dev),
+                 torch.zeros(B, H, dv // cb, state_block_floats(d, cb), device=dev), torch.empty(n, H * dv, device=dev))
+                for _ in range(4 if L == 1 else 1)]
+        ms = _timed([(lambda t=t: k.matrix_memory_scan(t[0], 0, H * d, 2 * H * d, t[1], bias, t[2], cu, sl, t[3], num_heads=H, dim=d,
+                                                       v_dim=dv, columns=cb, cap=15.0, q_scale=d ** -0.5, max_q_len=L)) for t in sets])
+        if L == 1:
+            mem_row(f"memory_scan_lekilix_decode_{B}", ms, B * 2 * H * (d * dv + d) * 4)
+        else:
+            flop_row(f"memory_scan_lekilix_prefill_{L}", ms, 4.0 * L * H * d * (dv + 1))
+            gate = sets[0][0][:, 2 * H * d + H * dv:]
+            wn = torch.ones(H * dv, device=dev)
+            o16 = torch.empty(n, H * dv, device=dev, dtype=bf)
+            ms = _timed([lambda: k.head_norm_gate_act(sets[0][3], wn, gate, o16, num_heads=1, eps=1e-6, gate_act="sigmoid")] * 4)
+            mem_row("norm_over_all_heads_gate", ms, n * H * dv * (4 + 2 + 2))
+            ms = _timed([lambda: k.head_norm_gate(sets[0][3], wn, gate, o16, num_heads=H, eps=1e-6)] * 4)
+            mem_row("head_norm_gate_lekilix", ms, n * H * dv * (4 + 2 + 2))
+        del sets
+    k.check_device_status()
+    return out
+
+
 def run_senadra(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
     """The kernels of the Senadra design alone, each beside its like kernel of another path at equal size (16 heads of 128 on
     8 KV heads, chunks of 2,048 positions; recurrences of 16 value heads 128 x 128 on 8 query/key heads; latents of 512 + 64):

@@ -11,7 +11,9 @@ bfloat16 matrix-product peak.
 """
 from __future__ import annotations
 
+import copy
 import json
+import math
 import os
 import random
 import statistics
@@ -117,7 +119,43 @@ SENADRA_SHAPES: Dict[str, dict] = {
     "s4k": _senadra_shape(4096, 32, 18432),
 }
 EQUAL_QWEN3.update({"s2k": _qwen3_shape(2048, 16, 8, 8192), "s4k": _qwen3_shape(4096, 32, 8, 12288)})
-DESIGN_SHAPES = {"galodra": GALODRA_SHAPES, "lekilix": LEKILIX_SHAPES, "senadra": SENADRA_SHAPES}
+def _nogelorn_shape(width, heads, experts, top, expert_ff, vocab=32768, window=4096, keep=128):
+    """Six layers of which the first two run twice (eight layer runs, as the shapes beside it): a side-by-side layer (sliding-
+    window attention of 128-wide heads on 8 key/value heads beside linear attention with a decay per key channel, half as
+    many heads, 128 deep and 128 wide), attention with kept first keys, a sink and a gate per head, and linear attention with
+    a constant decay per head (half as many heads, 128 deep and 256 wide: the state of the Lekilix memory beside it);
+    experts with one more that every token uses (so ``top`` + 1 are active)."""
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                          "rot": {"dims": 64, "base": 1000000.0,
+                                                  "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+                                          "mask": {"size": window, "keep_first": keep}}}
+    left = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 0.09, "mask": {"size": window},
+            "rot": {"dims": 128, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    par = {"type": "parallel", "mixer": {"left": left, "left_scale": 0.6, "right_scale": 0.9,
+                                         "right": {"heads": heads // 2, "dim": 128, "vdim": 128, "tau": 16.0, "decay_rank": 16}}}
+    nh = heads // 2
+    lin = {"type": "lightning", "mixer": {"heads": nh, "dim": 128, "vdim": 256,
+                                          "decay": [math.exp(-0.5 * (i + 1) / nh) for i in range(nh)]}}
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}, "shared": {"ff": expert_ff}}
+    order = [par, att, lin, att, lin, att]
+    return {"architecture": "Nogelorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": width ** 0.5},
+            "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": [dict(type=l["type"], mixer=copy.deepcopy(l["mixer"]), mlp=copy.deepcopy(mlp)) for l in order]}
+
+
+# Nogelorn shapes with layer sizes of real models; beside each the Lekilix shape of equal width, heads, layer runs and active
+# experts (its closest relative in the framework: a looped stretch, experts, recurrences beside windowed attention with a sink)
+# and the Qwen3 dense shape of equal active size.
+NOGELORN_SHAPES: Dict[str, dict] = {
+    "n2k-moe": _nogelorn_shape(2048, 16, 64, 5, 1408),
+    "n4k-moe": _nogelorn_shape(4096, 32, 64, 5, 2048),
+}
+EQUAL_QWEN3.update({"n2k-moe": _qwen3_shape(2048, 16, 8, 6 * 1408), "n4k-moe": _qwen3_shape(4096, 32, 8, 6 * 2048)})
+EQUAL_LEKILIX: Dict[str, dict] = {
+    "n2k-moe": _lekilix_shape(2048, 16, experts=64, top=6, expert_ff=1408),
+    "n4k-moe": _lekilix_shape(4096, 32, experts=64, top=6, expert_ff=2048),
+}
+DESIGN_SHAPES = {"galodra": GALODRA_SHAPES, "lekilix": LEKILIX_SHAPES, "senadra": SENADRA_SHAPES, "nogelorn": NOGELORN_SHAPES}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -158,10 +196,17 @@ def shape_config(name: str, layers: Optional[int] = None):
         if layers:
             raw["layers"] = raw["layers"][:layers]
         return senadra_config_from_dict(raw)
+    if name in NOGELORN_SHAPES:
+        from ..models.nogelorn import nogelorn_config_from_dict
+        raw = dict(NOGELORN_SHAPES[name])
+        if layers:
+            raw["layers"] = raw["layers"][:layers]
+            raw["loop"] = None if layers < raw["loop"]["stop"] else raw["loop"]
+        return nogelorn_config_from_dict(raw)
     try:
         raw = dict(SHAPES[name])
     except KeyError:
-        known = list(SHAPES) + list(GALODRA_SHAPES) + list(LEKILIX_SHAPES) + list(SENADRA_SHAPES)
+        known = list(SHAPES) + list(GALODRA_SHAPES) + list(LEKILIX_SHAPES) + list(SENADRA_SHAPES) + list(NOGELORN_SHAPES)
         raise ValueError(f"unknown shape '{name}' ({' | '.join(known)})") from None
     if layers:
         raw["num_hidden_layers"] = layers
@@ -174,12 +219,14 @@ def random_model(name: str, dtype: str = "bfloat16", device="cuda:0", seed: int 
     from ..engine.model import Model
     cfg = shape_config(name, layers)
     arch = ("Galodra" if name in GALODRA_SHAPES else "Lekilix" if name in LEKILIX_SHAPES else "Senadra" if name in SENADRA_SHAPES
-            else "Qwen3ForCausalLM")
+            else "Nogelorn" if name in NOGELORN_SHAPES else "Qwen3ForCausalLM")
     return Model.from_random(get_architecture(arch), cfg, seed=seed, dtype=dtype, device=device, norm_jitter=0.0)
 
 
 def accounting_for(cfg, dtype_bytes: int = 2):
     """Bytes and flops of a step for a configuration of any built-in architecture."""
+    if type(cfg).__name__ == "NogelornConfig":
+        return NogelornAccounting(cfg, dtype_bytes)
     if hasattr(cfg, "embedding_scale"):
         return LekilixAccounting(cfg, dtype_bytes)
     if hasattr(cfg, "residual_mult"):
@@ -301,6 +348,80 @@ class LekilixAccounting:
                 total += 4.0 * m.heads * m.dim * pairs
             else:
                 total += 4.0 * tokens * m.heads * m.dim * (m.vdim + 1)         # the update and the read-out of every token
+        return total
+
+
+class NogelornAccounting:
+    """Bytes and flops of a Nogelorn step, layer run by layer run (a layer of the looped stretch counts every time it runs).  A
+    decode step reads every dense weight once per run, of the experts those that the batch is expected to reach plus the
+    shared one, of a K/V cache the cells inside the window and the kept first ones, and reads and writes every recurrence's
+    float32 state."""
+
+    def __init__(self, cfg, dtype_bytes: int = 2):
+        self.cfg, self.b = cfg, dtype_bytes
+        self.head_w = cfg.vocab * cfg.width
+
+    @staticmethod
+    def _attention_w(w, m, gate: bool):
+        return w * (m.heads + m.kv_heads) * m.dim + w * m.kv_heads * m.vdim + m.heads * m.vdim * w + (w * m.heads if gate else 0)
+
+    @staticmethod
+    def _linear_w(w, m, rank: int = 0):
+        return w * (2 * m.heads * m.dim + 2 * m.heads * m.vdim) + m.heads * m.vdim * w + rank * (w + m.heads * m.dim)
+
+    def _layer(self, lc, batch: int):
+        """(weights read by a step of ``batch`` tokens, weights a token multiplies with) of one layer run."""
+        w, m = self.cfg.width, lc.mixer
+        if lc.type == "attention":
+            mix = self._attention_w(w, m, True)
+        elif lc.type == "lightning":
+            mix = self._linear_w(w, m)
+        else:
+            mix = self._attention_w(w, m.left, False) + self._linear_w(w, m.right, m.right.rank)
+        if lc.mlp is None:
+            return mix, mix
+        if lc.mlp.kind == "dense":
+            return mix + 3 * w * lc.mlp.ff, mix + 3 * w * lc.mlp.ff
+        e, top = lc.mlp.experts, lc.mlp.top
+        reached = e * (1.0 - (1.0 - top / e) ** batch)
+        fixed = w * e + 3 * w * lc.mlp.shared_ff
+        return mix + fixed + reached * 3 * w * lc.mlp.ff, mix + fixed + top * 3 * w * lc.mlp.ff
+
+    def _runs(self):
+        return [self.cfg.layers[i] for i, _ in self.cfg.run_order()]
+
+    @staticmethod
+    def _members(lc):
+        """(attention members, recurrent members) of a layer."""
+        if lc.type == "attention":
+            return [lc.mixer], []
+        if lc.type == "lightning":
+            return [], [lc.mixer]
+        return [lc.mixer.left], [lc.mixer.right]
+
+    def decode_bytes(self, batch: int, ctx_avg: float) -> float:
+        total = self.head_w * self.b
+        for lc in self._runs():
+            total += self._layer(lc, batch)[0] * self.b
+            att, rec = self._members(lc)
+            for m in att:
+                keys = min(ctx_avg, m.window + m.keep_first) if m.window else ctx_avg
+                total += batch * keys * m.kv_heads * (m.dim + m.vdim) * self.b
+            for m in rec:
+                total += batch * 2 * m.heads * m.dim * m.vdim * 4
+        return total
+
+    def prefill_flops(self, tokens: int) -> float:
+        total = 2.0 * self.head_w
+        for lc in self._runs():
+            total += 2.0 * tokens * self._layer(lc, 1)[1]
+            att, rec = self._members(lc)
+            for m in att:
+                w = m.window or tokens
+                pairs = tokens * (tokens + 1) / 2 if tokens <= w else w * (w + 1) / 2 + (tokens - w) * (w + m.keep_first)
+                total += 2.0 * m.heads * (m.dim + m.vdim) * pairs
+            for m in rec:
+                total += 4.0 * tokens * m.heads * m.dim * m.vdim               # the update and the read-out of every token
         return total
 
 
@@ -597,9 +718,13 @@ def design_comparison(names: Sequence[str], batches: Sequence[int], prefill_toke
     out = {}
     for name in names:
         row = {}
-        for side in (design, "qwen3"):
+        for side in (design, "lekilix", "qwen3") if design == "nogelorn" else (design, "qwen3"):
             if side == design:
                 model = random_model(name, "bfloat16", device)
+            elif side == "lekilix":
+                from ..models.lekilix import lekilix_config_from_dict
+                model = Model.from_random(get_architecture("Lekilix"), lekilix_config_from_dict(EQUAL_LEKILIX[name]), seed=0,
+                                          dtype="bfloat16", device=device, norm_jitter=0.0)
             else:
                 model = Model.from_random(get_architecture("Qwen3ForCausalLM"), qwen3_config_from_dict(EQUAL_QWEN3[name]), seed=0,
                                           dtype="bfloat16", device=device, norm_jitter=0.0)

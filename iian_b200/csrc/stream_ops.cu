@@ -76,6 +76,30 @@ __global__ void weighted_sum2_kernel(const A * __restrict__ x, float a, const A 
     out[idx] = from_f32<A>(fmaf(a, to_f32(x[idx]), b * to_f32(y[idx])));
 }
 
+// the same with a block per (token, head), for heads (or whole rows) of many entries
+template <typename A>
+__global__ void head_norm_gate_block_kernel(const float * __restrict__ x, const float * __restrict__ w, const A * __restrict__ g,
+                                            long long ld_g, A * __restrict__ out, int heads, int dv, float eps, int gate_act) {
+    pdl_wait();
+    __shared__ float scratch[32];
+    const long long item = blockIdx.x;
+    const long long t = item / heads;
+    const int h = (int) (item - t * heads);
+    const float * xr = x + item * dv;
+    float ss = 0.0f;
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) ss += xr[d] * xr[d];
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float) dv + eps);
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+        float v = xr[d] * inv * w[h * dv + d];
+        if (g != nullptr) {
+            const float z = to_f32(g[t * ld_g + h * dv + d]);
+            v *= gate_act == 1 ? z * sigmoid_f32(z) : sigmoid_f32(z);
+        }
+        out[item * dv + d] = from_f32<A>(v);
+    }
+}
+
 }  // namespace iian
 
 using namespace iian;
@@ -110,6 +134,12 @@ IIAN_API int iian_head_norm_gate_act(const float * x, const float * w, const voi
     const long long items = (long long) N * heads;
     if (items <= 0) return IIAN_OK;
     if (dv <= 0 || (gate_act != 0 && gate_act != 1)) return IIAN_ERR_SHAPE;
+    if (dv >= 1024 && items <= 0x7fffffff) {          // long rows: a block each
+        const int threads = dv >= 4096 ? 512 : 256;
+        if (act_dtype == IIAN_F32) return iian_launch(head_norm_gate_block_kernel<float>, dim3((unsigned) items), dim3(threads), 0, stream, x, w, (const float *) g, ld_g, (float *) out, heads, dv, eps, gate_act);
+        if (act_dtype == IIAN_BF16) return iian_launch(head_norm_gate_block_kernel<__nv_bfloat16>, dim3((unsigned) items), dim3(threads), 0, stream, x, w, (const __nv_bfloat16 *) g, ld_g, (__nv_bfloat16 *) out, heads, dv, eps, gate_act);
+        return IIAN_ERR_DTYPE;
+    }
     const int warps = 4;
     const unsigned blocks = (unsigned) ((items + warps - 1) / warps);
     if (act_dtype == IIAN_F32) return iian_launch(head_norm_gate_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, x, w, (const float *) g, ld_g, (float *) out, items, heads, dv, eps, gate_act);

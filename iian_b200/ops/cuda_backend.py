@@ -1660,7 +1660,7 @@ class CudaKernels:
                    q_scale: float, head_decay: Optional[torch.Tensor] = None, z: Optional[torch.Tensor] = None,
                    z_bias: Optional[torch.Tensor] = None, tau: float = 1.0, max_q_len: int = 0) -> None:
         """Walk every sequence's tokens of this step through ``S <- diag(a) S + k v^T``, ``o = S^T q`` from and into ``state``
-        [slots, heads, dim, v_dim] (float32).  ``proj`` rows hold q, k, v at the given column offsets (``activation`` ``silu``:
+        [slots, heads, ceil(v_dim / 16), dim, 16] (float32, blocks of 16 columns).  ``proj`` rows hold q, k, v at the given column offsets (``activation`` ``silu``:
         all three pass it first); q is multiplied by ``q_scale``.  The decay is ``head_decay`` [heads] (one constant per head)
         or, per token and key channel, ``sigmoid(z + z_bias)^(1 / tau)`` with ``z`` float32 [N, heads * dim] (may be a column
         slice).  ``out`` float32 [N, heads * v_dim]."""
@@ -1668,11 +1668,18 @@ class CudaKernels:
         pp, ld = self._rows(proj, "projections")
         zp, ld_z = self._rows(z, "decay pre-activations")
         s = cu_q.numel() - 1
-        if out.shape != (n, num_heads * v_dim) or state_slots.numel() != s or state.dim() != 4 or state.shape[1:] != (num_heads, dim, v_dim) \
+        if out.shape != (n, num_heads * v_dim) or state_slots.numel() != s or state.dim() != 5 or state.shape[1:] != (num_heads, -(-v_dim // 16), dim, 16) \
                 or (head_decay is None) == (z is None) or (head_decay is not None and head_decay.numel() != num_heads) \
                 or (z is not None and (z.shape != (n, num_heads * dim) or z.dtype != torch.float32)) \
                 or (z_bias is not None and z_bias.numel() != num_heads * dim) or activation not in (None, "silu"):
             raise KernelError("decay_scan: shapes do not fit")
+        per_lane = int(os.environ.get("IIAN_DECAY_SCAN_PER_LANE", "0"))
+        if per_lane and not getattr(self, "_decay_per_lane_set", False):
+            lib = _build.load("decay_scan")
+            lib.iian_decay_scan_set_entries_per_lane.argtypes = [c_int]
+            lib.iian_decay_scan_set_entries_per_lane.restype = None
+            lib.iian_decay_scan_set_entries_per_lane(per_lane)
+            self._decay_per_lane_set = True
         fn = _fn("decay_scan", "iian_decay_scan",
                  [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_void_p,
                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])

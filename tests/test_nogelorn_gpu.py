@@ -72,7 +72,7 @@ def test_weighted_sum_and_heads_norm_with_either_gate(dtype):
     out = torch.empty(7, 96, dtype=DT[dtype], device=DEV)
     K().weighted_sum2(a.to(DEV), 0.7, b.to(DEV), 1.3, out)
     close(out, 0.7 * a.double() + 1.3 * b.double(), dtype, "weighted sum of two", rel16=8e-3)
-    for heads, dv, act in ((1, 120, "sigmoid"), (3, 40, "silu"), (5, 12, "silu"), (2, 128, "sigmoid")):
+    for heads, dv, act in ((1, 120, "sigmoid"), (3, 40, "silu"), (5, 12, "silu"), (2, 128, "sigmoid"), (1, 2048, "sigmoid"), (2, 1100, "silu")):
         x = torch.randn(6, heads * dv, generator=g) * 4
         w = torch.randn(heads * dv, generator=g)
         wide = torch.randn(6, heads * dv + 8, generator=g).to(DT[dtype])
@@ -211,7 +211,7 @@ def test_attention_sees_window_kept_keys_and_sink_exactly(dtype, nh, nkv, dk, dv
     if outside >= keep:
         assert p[:, n - 1, outside].max() == 0 and p[:, n - 2, outside].max() > 0.2     # one token earlier it was still seen
     elif outside >= 0:
-        assert p[:, n - 1, outside].max() > 0.01                                        # behind the window, but a kept key
+        assert p[:, n - 2, outside].max() > 0.2 and p[:, n - 1, outside].max() > 0      # behind the window, but a kept key
     if len(marks) == 4:
         assert p[:, n - 3, keep - 1].max() > 0.2 and p[:, n - 4, keep].max() == 0       # the last kept key; the first forgotten one
     bt = torch.full((1, max(64, c.order.numel())), -1, dtype=torch.int32)
@@ -272,7 +272,7 @@ def test_decayed_scan_cut_into_steps_with_slots_used_again(dtype, H, d, dv, per_
     tau, q_scale, act = 3.0, d ** -0.5, not per_channel
     want = [_plain_scan(p.double()[:, 4:], H, d, dv, act, q_scale, None if per_channel else head_decay.double(), z.double(), bias.double(), tau)[0]
             for p, z in zip(projs, zs)]
-    state = torch.zeros(4, H, d, dv, device=DEV)
+    state = torch.zeros(4, H, -(-dv // 16), d, 16, device=DEV)
     slots = [2, 0, 3]
     fed = [0, 0, 0]
     got = [torch.zeros(n, H * dv) for n in lengths]
