@@ -139,7 +139,7 @@ def cmd_bench(argv: List[str]) -> int:
                               "batching of many requests of random lengths, half behind a shared prefix.")
     o.positional("model", "model folder (or leave out and name a --shape with random weights)", nargs="?")
     o.group("Benchmark")
-    o.add("--shape", "Random-weight model of a named shape instead of a folder: tinyA | tinyB | 0.6b | 8b | 32b | g2k-dense | g2k-moe | g4k-dense | l2k-dense | l2k-moe | l4k-dense | s2k | s4k", "NAME", "", str)
+    o.add("--shape", "Random-weight model of a named shape instead of a folder: tinyA | tinyB | 0.6b | 8b | 32b | g2k-dense | g2k-moe | g4k-dense | l2k-dense | l2k-moe | l4k-dense | s2k | s4k | n2k-moe | n4k-moe", "NAME", "", str)
     o.add("--layers", "With --shape: run this many layers of the shape (0 = all)", "N", 0, int)
     o.add("--concurrency", "Comma-separated concurrency levels", "LIST", "1,4,16", str)
     o.add("--prompt-tokens", "Prompt length per request", "N", 256, int)
