@@ -74,16 +74,18 @@ struct AttnParams {
 // first key of the chunk that position `pos` lies in
 __device__ __forceinline__ int chunk_start(int pos, int chunk) { return chunk > 0 ? pos - pos % chunk : 0; }
 // the gate's factor for two neighbouring output columns of row (token, head): sigmoid in float32
+template <bool KEPT>
 __device__ __forceinline__ float2 gate_pair(const AttnParams & p, size_t token, int col) {
-    if (p.gate_per_head) {         // one number per head: gate_per_head holds the head's size
+    if (KEPT && p.gate_per_head) {         // one number per head: gate_per_head holds the head's size
         const float v = 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[token * p.ld_gate + col / p.gate_per_head])));
         return make_float2(v, v);
     }
     const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p.gate + token * p.ld_gate + col));
     return make_float2(1.0f / (1.0f + __expf(-g.x)), 1.0f / (1.0f + __expf(-g.y)));
 }
+template <bool KEPT>
 __device__ __forceinline__ float gate_one(const AttnParams & p, size_t token, int col) {
-    if (p.gate_per_head) col /= p.gate_per_head;
+    if (KEPT && p.gate_per_head) col /= p.gate_per_head;
     return 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[token * p.ld_gate + col])));
 }
 
@@ -159,7 +161,8 @@ __device__ __forceinline__ void dk_tma_4d(unsigned dst, const CUtensorMap * map,
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(w), "r"(bar) : "memory");
 }
 
-template <int HD, int NW>
+// KEPT: the forms with kept first keys and a gate per head are instances of their own, so that the others stay as they were
+template <int HD, int NW, bool KEPT = false>
 __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnParams p) {
     constexpr int BM = 16 * NW;
     constexpr int CH = HD / 8;                 // 16-byte chunks per row
@@ -194,9 +197,9 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
     const int tile_lo = k_lo / BN, tile_hi = k_hi / BN;
     // kept first keys: their tiles (those wholly before the window's first tile) are walked first, as virtual tiles
     // vlo .. tile_lo - 1; phys() gives the tile of the cache a virtual tile stands for
-    const int n_keep = (p.keep_first > 0 && p.window > 0) ? min((p.keep_first + BN - 1) / BN, tile_lo) : 0;
+    const int n_keep = (KEPT && p.keep_first > 0 && p.window > 0) ? min((p.keep_first + BN - 1) / BN, tile_lo) : 0;
     const int vlo = tile_lo - n_keep;
-    auto phys = [&](int v) { return v >= tile_lo ? v : v - vlo; };
+    auto phys = [&](int v) { return !KEPT || v >= tile_lo ? v : v - vlo; };
     const int n_tiles = tile_hi - vlo + 1;
     const int per = (n_tiles + p.n_split - 1) / p.n_split;
     const int tile_begin = vlo + split * per;
@@ -352,7 +355,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
                     for (int e = 0; e < 4; e++) {
                         const int h = e >> 1;
                         const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window || j < p.keep_first) && j >= row_lo[h];
+                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window || (KEPT && j < p.keep_first)) && j >= row_lo[h];
                         if (!vis) sc[nt][e] = -INFINITY;
                     }
                 }
@@ -438,7 +441,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
                 const int d = dt * 8 + 2 * t_;
                 float2 v = make_float2(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
                 if (p.gate != nullptr) {
-                    const float2 gt = gate_pair(p, (size_t) (q0 + tok), head * HD + d);
+                    const float2 gt = gate_pair<KEPT>(p, (size_t) (q0 + tok), head * HD + d);
                     v.x *= gt.x; v.y *= gt.y;
                 }
                 *reinterpret_cast<__nv_bfloat162 *>(dst + d) = __floats2bfloat162_rn(v.x, v.y);
@@ -482,7 +485,7 @@ __global__ void __launch_bounds__(NW * 32, 3) attention_mma_kernel(const AttnPar
 // cp.async copies with a looked-up address per row: the copies of a tile are sixteen instructions of one warp rather
 // than sixteen of every thread, and they do not pass through the load/store units that bound the cp.async form at
 // three quarters of the memory bandwidth.  Head size 128, pages of 8 to 64 tokens.
-template <int HD, bool CLUSTER, bool FUSED, int STAGES, bool TMA>
+template <int HD, bool CLUSTER, bool FUSED, int STAGES, bool TMA, bool KEPT = false>
 __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_kernel(const AttnParams p, const __grid_constant__ KvMaps maps) {
     constexpr int NW = 4, BM = 16;
     constexpr int CH = HD / 8, KS = HD / 16, DT = HD / 8;
@@ -517,9 +520,9 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
     const int tile_lo = k_lo / BN, tile_hi = k_hi / BN;
     // kept first keys: their tiles (those wholly before the window's first tile) are walked first, as virtual tiles
     // vlo .. tile_lo - 1; phys() gives the tile of the cache a virtual tile stands for
-    const int n_keep = (p.keep_first > 0 && p.window > 0) ? min((p.keep_first + BN - 1) / BN, tile_lo) : 0;
+    const int n_keep = (KEPT && p.keep_first > 0 && p.window > 0) ? min((p.keep_first + BN - 1) / BN, tile_lo) : 0;
     const int vlo = tile_lo - n_keep;
-    auto phys = [&](int v) { return v >= tile_lo ? v : v - vlo; };
+    auto phys = [&](int v) { return !KEPT || v >= tile_lo ? v : v - vlo; };
     const int n_tiles = tile_hi - vlo + 1;
     const int per = (n_tiles + p.n_split - 1) / p.n_split;
     const int tile_begin = vlo + split * per;
@@ -806,7 +809,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
                     for (int e = 0; e < 4; e++) {
                         const int h = e >> 1;
                         const int j = key0 + nt * 8 + 2 * t_ + (e & 1);
-                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window || j < p.keep_first) && j >= row_lo[h];
+                        const bool vis = row_ok[h] && j <= row_tok[h] && (p.window == 0 || row_tok[h] - j < p.window || (KEPT && j < p.keep_first)) && j >= row_lo[h];
                         if (!vis) sc[nt][e] = -INFINITY;
                     }
                 }
@@ -926,7 +929,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
                 *reinterpret_cast<float2 *>(cO + mr * HD + d) = make_float2(v0, v1);
             else if (p.n_split == 1) {
                 float2 gt = make_float2(1.0f, 1.0f);
-                if (p.gate != nullptr) gt = gate_pair(p, (size_t) (q0 + mR / G), (kvh * G + mR % G) * HD + d);
+                if (p.gate != nullptr) gt = gate_pair<KEPT>(p, (size_t) (q0 + mR / G), (kvh * G + mR % G) * HD + d);
                 *reinterpret_cast<__nv_bfloat162 *>(p.out + row_idx * HD + d) = __floats2bfloat162_rn(v0 * inv * gt.x, v1 * inv * gt.y);
             } else
                 *reinterpret_cast<float2 *>(p.part_o + (row_idx * p.n_split + split) * HD + d) = make_float2(v0 * inv, v1 * inv);
@@ -962,7 +965,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
             const int R = row0 + r;
             const size_t ri = (size_t) (q0 + R / G) * p.nh + kvh * G + R % G;
             float res = l > 0.0f ? v / l : 0.0f;
-            if (p.gate != nullptr) res *= gate_one(p, (size_t) (q0 + R / G), (kvh * G + R % G) * HD + d);
+            if (p.gate != nullptr) res *= gate_one<KEPT>(p, (size_t) (q0 + R / G), (kvh * G + R % G) * HD + d);
             p.out[ri * HD + d] = __float2bfloat16_rn(res);
         }
         cluster.sync();                                      // nobody leaves while its shared memory is being read
@@ -1004,7 +1007,7 @@ __global__ void __launch_bounds__(128, STAGES == 2 ? 3 : 2) attention_decode_ker
 #pragma unroll
         for (int c = 0; c < HD / 8; c += 2) {
             float2 gt = make_float2(1.0f, 1.0f);
-            if (p.gate != nullptr) gt = gate_pair(p, (size_t) (q0 + mR / G), (kvh * G + mR % G) * HD + mpart * (HD / 8) + c);
+            if (p.gate != nullptr) gt = gate_pair<KEPT>(p, (size_t) (q0 + mR / G), (kvh * G + mR % G) * HD + mpart * (HD / 8) + c);
             *reinterpret_cast<__nv_bfloat162 *>(dst + c) = __floats2bfloat162_rn(acc[c] * inv * gt.x, acc[c + 1] * inv * gt.y);
         }
     }
@@ -1053,21 +1056,21 @@ static int kv_map_for(const void * base, int num_pages, int nkv, int page_size, 
     return IIAN_OK;
 }
 
-template <int HD, bool CLUSTER, bool FUSED, int STAGES, bool TMA>
+template <int HD, bool CLUSTER, bool FUSED, int STAGES, bool TMA, bool KEPT>
 static int launch_decode_st(const AttnParams & p, const KvMaps & maps, int S, int max_rows, cudaStream_t stream) {
     const size_t smem = (size_t) 16 * HD * 2 + 2 * STAGES * BN * HD * 2 + (TMA ? 1024 : 0);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA, KEPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return 1000 + (int) e;
         configured = true;
     }
     dim3 grid((max_rows + 15) / 16, p.nkv, S * p.n_split);
-    if (!CLUSTER) return iian_launch(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA>, grid, dim3(128), smem, stream, p, maps);
+    if (!CLUSTER) return iian_launch(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA, KEPT>, grid, dim3(128), smem, stream, p, maps);
     if (p.n_split > 8) {                                   // clusters of 9 to 16 CTAs have to be asked for
         static bool allowed = false;
         if (!allowed) {
-            cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA, KEPT>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             if (e != cudaSuccess) return 1000 + (int) e;
             allowed = true;
         }
@@ -1084,7 +1087,7 @@ static int launch_decode_st(const AttnParams & p, const KvMaps & maps, int S, in
     attr[0].val.clusterDim.z = (unsigned) p.n_split;       // the parts of one row tile are consecutive in z
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA>, p, maps);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD, CLUSTER, FUSED, STAGES, TMA, KEPT>, p, maps);
     return e == cudaSuccess ? IIAN_OK : 1000 + (int) e;
 }
 
@@ -1102,7 +1105,7 @@ static int decode_sm_count() {
 
 static int g_decode_stages = 2;
 static int g_unsplit_stages = 0;        // 0: the rule below; 2 or 3: that many for unsplit keys
-template <int HD, bool CLUSTER, bool FUSED = false>
+template <int HD, bool CLUSTER, bool FUSED = false, bool KEPT = false>
 static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
     // unsplit keys mean many sequences, each CTA walking a whole context: the deeper pipeline pays there
     bool deep = g_decode_stages == 3;
@@ -1127,12 +1130,12 @@ static int launch_decode(const AttnParams & p, int S, int max_rows, cudaStream_t
             int rc = kv_map_for(p.k_cache, p.num_pages, p.nkv, ps, &maps.k);
             if (rc == IIAN_OK) rc = kv_map_for(p.v_cache, p.num_pages, p.nkv, ps, &maps.v);
             if (rc != IIAN_OK) return rc;
-            if (deep) return launch_decode_st<HD, CLUSTER, FUSED, 3, true>(p, maps, S, max_rows, stream);
-            return launch_decode_st<HD, CLUSTER, FUSED, 2, true>(p, maps, S, max_rows, stream);
+            if (deep) return launch_decode_st<HD, CLUSTER, FUSED, 3, true, KEPT>(p, maps, S, max_rows, stream);
+            return launch_decode_st<HD, CLUSTER, FUSED, 2, true, KEPT>(p, maps, S, max_rows, stream);
         }
     }
-    if (deep) return launch_decode_st<HD, CLUSTER, FUSED, 3, false>(p, maps, S, max_rows, stream);
-    return launch_decode_st<HD, CLUSTER, FUSED, 2, false>(p, maps, S, max_rows, stream);
+    if (deep) return launch_decode_st<HD, CLUSTER, FUSED, 3, false, KEPT>(p, maps, S, max_rows, stream);
+    return launch_decode_st<HD, CLUSTER, FUSED, 2, false, KEPT>(p, maps, S, max_rows, stream);
 }
 
 // merge the n_split partial results of every (token, head): one warp per row
@@ -1164,18 +1167,18 @@ __global__ void attention_combine_kernel(const float * __restrict__ part_o, cons
     for (int k = 0; k < HD / 32; k++) out[(size_t) row * HD + lane + 32 * k] = __float2bfloat16_rn(acc[k] * inv);
 }
 
-template <int HD, int NW>
+template <int HD, int NW, bool KEPT = false>
 static int launch_attention(const AttnParams & p, int S, int max_rows, cudaStream_t stream) {
     constexpr int BM = 16 * NW;
     const size_t smem = (size_t) 4 * BN * HD * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_mma_kernel<HD, NW, KEPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return 1000 + (int) e;
         configured = true;
     }
     dim3 grid((max_rows + BM - 1) / BM, p.nkv, S * p.n_split);
-    attention_mma_kernel<HD, NW><<<grid, NW * 32, smem, stream>>>(p);
+    attention_mma_kernel<HD, NW, KEPT><<<grid, NW * 32, smem, stream>>>(p);
     return iian_launch_status();
 }
 
@@ -1309,7 +1312,11 @@ IIAN_API int iian_attention_mma_kept(
     p.gate_per_head = gate != nullptr && gate_per_head ? hd : 0;
     const int max_rows = max_q_len * (nh / nkv);
     int rc;
-    if (cluster) rc = hd == 128 ? launch_decode<128, true>(p, S, max_rows, stream) : launch_decode<64, true>(p, S, max_rows, stream);
+    if (p.keep_first > 0 || p.gate_per_head) {
+        if (cluster) rc = hd == 128 ? launch_decode<128, true, false, true>(p, S, max_rows, stream) : launch_decode<64, true, false, true>(p, S, max_rows, stream);
+        else if (hd == 128) rc = small_tiles ? launch_decode<128, false, false, true>(p, S, max_rows, stream) : launch_attention<128, 4, true>(p, S, max_rows, stream);
+        else rc = small_tiles ? launch_decode<64, false, false, true>(p, S, max_rows, stream) : launch_attention<64, 4, true>(p, S, max_rows, stream);
+    } else if (cluster) rc = hd == 128 ? launch_decode<128, true>(p, S, max_rows, stream) : launch_decode<64, true>(p, S, max_rows, stream);
     else if (hd == 128) rc = small_tiles ? launch_decode<128, false>(p, S, max_rows, stream) : launch_attention<128, 4>(p, S, max_rows, stream);
     else rc = small_tiles ? launch_decode<64, false>(p, S, max_rows, stream) : launch_attention<64, 4>(p, S, max_rows, stream);
     if (rc != IIAN_OK || n_split == 1 || small_tiles) return rc;      // the decode form merges its parts itself

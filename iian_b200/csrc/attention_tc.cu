@@ -178,6 +178,8 @@ __host__ __device__ constexpr unsigned at_idesc(int m, int n, bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((unsigned) (n >> 3) << 17) | ((unsigned) (m >> 4) << 24);
 }
 
+// KEPT: the form with kept first keys and a gate per head is an instance of its own, so that the other stays as it was
+template <bool KEPT>
 __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const TcAttnParams p) {
     extern __shared__ __align__(1024) unsigned char at_smem_raw[];
@@ -207,8 +209,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
     const int k_lo = p.window > 0 ? max(0, pos0 + tok_min - p.window + 1)
                                   : p.chunk > 0 ? (pos0 + tok_min) - (pos0 + tok_min) % p.chunk : 0;
     const int tile_lo = k_lo / AT_BN, tile_hi = k_hi / AT_BN;
-    const int n_keep = (p.keep_first > 0 && p.window > 0) ? min((p.keep_first + AT_BN - 1) / AT_BN, tile_lo) : 0;
-    auto phys = [&](int i) { return i < n_keep ? i : tile_lo + i - n_keep; };        // the cache tile of the i-th tile walked
+    const int n_keep = (KEPT && p.keep_first > 0 && p.window > 0) ? min((p.keep_first + AT_BN - 1) / AT_BN, tile_lo) : 0;
+    auto phys = [&](int i) { return KEPT && i < n_keep ? i : tile_lo + i - n_keep; };        // the cache tile of the i-th tile walked
     const int n_tiles = tile_hi - tile_lo + 1 + n_keep;
     const int n_grp[2] = {k_hi_a / AT_BN - tile_lo + 1 + n_keep, has_b ? n_tiles : 0};
     const int * bt = p.block_table + (size_t) s * p.max_blocks;
@@ -411,8 +413,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
             int lo = p.window > 0 ? max(0, row_pos - p.window + 1 - key0) : max(0, row_lo - key0);
             // kept first keys in this tile: columns [0, kept); where they reach the window's first column the row sees one
             // stretch from column 0, else two (columns [kept, lo) stay hidden)
-            const int kept = max(0, p.keep_first - key0);
-            if (kept >= lo) lo = 0;
+            const int kept = KEPT ? max(0, p.keep_first - key0) : 0;
+            if (KEPT && kept >= lo) lo = 0;
             if (p.pen1 != nullptr) {                // the distance penalty, in units of raw scores (masked keys are set below)
                 const float d0 = (float) (row_pos - key0);
 #pragma unroll
@@ -423,7 +425,7 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                 if (two_sided) {
 #pragma unroll
                     for (int j = 0; j < AT_BN; j++)
-                        if ((j < lo && j >= kept) || j > hi) v[j] = 0xff800000u;        // -inf
+                        if ((j < lo && (!KEPT || j >= kept)) || j > hi) v[j] = 0xff800000u;        // -inf
                 } else {
 #pragma unroll
                     for (int j = 0; j < AT_BN; j++)
@@ -505,10 +507,10 @@ __global__ void __launch_bounds__(AT_THREADS, 1) attention_tc_kernel(
                 if (row_ok) {
                     const int tok = R / G, head = kvh * G + R % G;
                     dst = p.out + ((size_t) (q0 + tok) * p.nh + head) * AT_HD;
-                    if (p.gate != nullptr && !p.gate_per_head) gsrc = p.gate + (size_t) (q0 + tok) * p.ld_gate + (size_t) head * AT_HD;
-                    if (p.gate != nullptr && p.gate_per_head) head_gate = 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(size_t) (q0 + tok) * p.ld_gate + head])));
+                    if (p.gate != nullptr && !(KEPT && p.gate_per_head)) gsrc = p.gate + (size_t) (q0 + tok) * p.ld_gate + (size_t) head * AT_HD;
+                    if (KEPT && p.gate != nullptr && p.gate_per_head) head_gate = 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(size_t) (q0 + tok) * p.ld_gate + head])));
                 }
-                inv *= head_gate;
+                if (KEPT) inv *= head_gate;
                 unsigned o[AT_HD];                  // the whole row at once: one wait for four loads
 #pragma unroll
                 for (int c0 = 0; c0 < AT_HD; c0 += 32) at_ld32(tO + lane_addr + (unsigned) c0, o + c0);
@@ -676,14 +678,17 @@ IIAN_API int iian_attention_tc_kept(const void * q, long long ld_q, const void *
     p.keep_first = keep_first;
     p.gate_per_head = gate != nullptr && gate_per_head ? 1 : 0;
     const size_t smem = (size_t) 6 * AT_TILE_BYTES + 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+    const bool kept = keep_first > 0 || p.gate_per_head;
+    static bool configured[2] = {false, false};
+    if (!configured[kept ? 1 : 0]) {
+        cudaError_t e = kept ? cudaFuncSetAttribute(attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem)
+                             : cudaFuncSetAttribute(attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
         if (e != cudaSuccess) return 1000 + (int) e;
-        configured = true;
+        configured[kept ? 1 : 0] = true;
     }
     const int max_rows = max_q_len * (nh / nkv);
     dim3 grid((max_rows + AT_ROWS - 1) / AT_ROWS, nkv, S);
-    attention_tc_kernel<<<grid, AT_THREADS, smem, stream>>>(mk, mv, p);
+    if (kept) attention_tc_kernel<true><<<grid, AT_THREADS, smem, stream>>>(mk, mv, p);
+    else attention_tc_kernel<false><<<grid, AT_THREADS, smem, stream>>>(mk, mv, p);
     return iian_launch_status();
 }
