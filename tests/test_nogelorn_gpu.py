@@ -183,13 +183,26 @@ def _plain_attention(c, nh, nkv, dv, scale, window, keep, sink, gate):
     (4, 2, 128, 128, 150, 0, 16), (4, 2, 128, 128, 150, 40, 16), (2, 2, 96, 96, 100, 33, 16), (4, 1, 64, 32, 48, 16, 8),
     (8, 2, 64, 64, 64, 70, 16), (4, 2, 128, 128, 150, 200, 16), (8, 1, 128, 128, 40, 129, 32)])
 def test_attention_sees_window_kept_keys_and_sink_exactly(dtype, nh, nkv, dk, dv, window, keep, page):
+    _attention_case(dtype, nh, nkv, dk, dv, window, keep, page, 300 if window else 1500)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh, nkv, dk, dv, window, keep, page, n", [
+    (8, 4, 64, 64, 136, 20, 16, 1400), (8, 2, 128, 128, 700, 200, 16, 2600), (4, 4, 128, 128, 96, 0, 16, 1200), (6, 2, 96, 96, 136, 20, 16, 1100),
+    (4, 2, 128, 128, 1024, 64, 16, 3000)])
+def test_attention_in_long_contexts(dtype, nh, nkv, dk, dv, window, keep, page, n):
+    """The same far behind the window: many key tiles are skipped between the kept keys and the window, decoded tokens split
+    their keys into parts, long portions run on the tcgen05 kernel."""
+    _attention_case(dtype, nh, nkv, dk, dv, window, keep, page, n)
+
+
+def _attention_case(dtype, nh, nkv, dk, dv, window, keep, page, n):
     """Keys are made to stand out by putting a multiple of a query into their cache cells: one just inside and one just outside
     the last token's window, one that is the last kept key and one right behind the kept keys (without a window: one at
     position 1, hundreds of tokens back).  Queries: a portion of the last 7 tokens, the same tokens one by one, the first ones,
     long portions.  Heads of 64 / 128 with equal sizes run on the tensor-core kernels in bfloat16 (kept keys, sink and gate inside
     them)."""
-    n = 300 if window else 1500                 # without a window: enough keys that decoding cuts them into several parts
-    w = window or n
+    w = window or n                             # without a window: enough keys that decoding cuts them into several parts
     inside, outside = (max(n - w, 1), n - w - 1) if window else (1, -1)
     c = _fill_cache(dtype, nh, nkv, dk, dv, plain.base_frequencies(min(dk, 16) // 2 * 2, 777.0), 1.0, True, list(range(n)), page,
                     seed=nh * dk, gate_cols=nh)
@@ -452,6 +465,10 @@ def test_long_decoding_and_a_far_key(folders, dtype):
     run_trace(folders[("G", dtype)], "G", dtype, reqs, want, trace_tail(reqs, 200), 256, "long decoding")
     reqs, want = requests_and_plain(folders, "I", dtype, [200], seed=91)
     run_trace(folders[("I", dtype)], "I", dtype, reqs, want, trace_tail(reqs, 190), 256, "long decoding")
+    for name, seed in (("J", 92), ("H", 93)):          # heads of 128 with kept keys, heads of 64 with a sink: the tensor-core kernels
+        reqs, want = requests_and_plain(folders, name, dtype, [300, 270], seed=seed)
+        run_trace(folders[(name, dtype)], name, dtype, reqs, want, trace_tail(reqs, 150), 320, "long decoding")
+        run_trace(folders[(name, dtype)], name, dtype, reqs, want, trace_mixed(reqs, 640, seed=5), 640, "long, mixed")
     d = folders[("G", dtype)] + "_far"
     if not os.path.isdir(d):
         cfg, w = plain.load_folder(folders[("G", dtype)])
