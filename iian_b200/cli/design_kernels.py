@@ -552,7 +552,7 @@ def run_nogelorn(peaks: dict, width: int = 2048, heads: int = 16) -> dict:
         n = B * L
         cu = torch.arange(0, n + 1, L, dtype=torch.int32, device=dev)
         sl = torch.arange(B, dtype=torch.int32, device=dev)
-        sets = [(torch.randn(n, wide, device=dev).to(bf) * 0.5, torch.randn(n, H * d, device=dev), torch.zeros(B, H, dv // 16, d, 16, device=dev),
+        sets = [(torch.randn(n, wide, device=dev).to(bf) * 0.5, torch.randn(n, H * d, device=dev), torch.zeros(B, H, dv // 16, 16, d, device=dev),
                  torch.empty(n, H * dv, device=dev)) for _ in range(4 if L == 1 else 1)]
         for tag, kw in (("head", {"head_decay": decay, "activation": "silu"}), ("channel", {"z_bias": zb, "tau": 16.0, "activation": None})):
             ms = _timed([(lambda t=t: k.decay_scan(t[0], 0, H * d, 2 * H * d, t[2], cu, sl, t[3], num_heads=H, dim=d, v_dim=dv, q_scale=1.0,

@@ -16,8 +16,9 @@
 // together, since only the update of s lies on the chain from token to token.  Every sum has an order fixed by (d, L), so the
 // result does not depend on how a sequence was cut into steps or what else is in the batch.
 //
-// The state is stored in blocks of 16 columns, [slot][head][block][d][16], so that a CTA's share is one contiguous piece; it
-// comes and goes through shared memory with 16-byte moves.
+// The state is stored column by column in blocks of 16 columns, [slot][head][block][16][d4] with d4 = d rounded up to a multiple
+// of 4: a CTA's share is one contiguous piece, a lane's entries are 16-byte pieces of its column, and the lanes of a column
+// read neighbouring pieces -- the state goes straight between global memory and registers.
 #include "common.cuh"
 
 namespace iian {
@@ -35,7 +36,7 @@ struct DecayScanParams {
     long long ld_z;
     const float * z_bias;         // f32 [H * d] or null
     float inv_tau;
-    float * state;                // f32 [slots, H, blocks, d, 16]
+    float * state;                // f32 [slots, H, blocks, 16, d4]
     const int * cu_q;             // i32 [S + 1]
     const int * state_slots;      // i32 [S]   (-1: padding sequence)
     float * out;                  // f32 [n, H * dv]
@@ -76,16 +77,16 @@ __global__ void decay_scan_kernel(const DecayScanParams p) {
     float * a_s = v_s + (size_t) p.chunk * kDsCols;      // only with a decay per channel
     const float a_head = per_channel ? 0.0f : p.head_decay[h];
 
-    // ---- the state: this CTA's block through shared memory into the lanes' registers ------------------------------------------
+    // ---- the state: a column is contiguous (d rounded up to a multiple of 4 floats), a lane's pieces are 16 bytes each ---------
     float s[EPL];
-    float * st = p.state + (((size_t) slot * H + h) * gridDim.x + blockIdx.x) * (size_t) d * kDsCols;
-    for (int idx = tid; idx < d * kDsCols / 4; idx += nthreads)
-        reinterpret_cast<float4 *>(smem)[idx] = reinterpret_cast<const float4 *>(st)[idx];
-    __syncthreads();
+    const int d4 = (d + 3) & ~3;
+    float * st = p.state + ((((size_t) slot * H + h) * gridDim.x + blockIdx.x) * kDsCols + col) * (size_t) d4;
 #pragma unroll
-    for (int e = 0; e < EPL; e++) {
-        const int i = 4 * ((e >> 2) * L + lane) + (e & 3);
-        s[e] = i < d ? smem[i * kDsCols + col] : 0.0f;
+    for (int g = 0; g < EPL / 4; g++) {
+        const int i4 = 4 * (g * L + lane);
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (col_ok && i4 < d4) v = *reinterpret_cast<const float4 *>(st + i4);
+        s[4 * g + 0] = v.x; s[4 * g + 1] = v.y; s[4 * g + 2] = v.z; s[4 * g + 3] = v.w;
     }
     const A * proj = (const A *) p.proj;
 
@@ -180,7 +181,6 @@ __global__ void decay_scan_kernel(const DecayScanParams p) {
     };
 
     if (VEC && r0 < r1) fetch(r0, min(p.chunk, r1 - r0));
-    __syncthreads();                                      // everyone has taken its share of the state out of shared memory
     // entries of a row beyond d (the lanes' padding) are zero for good
     for (int idx = tid; idx < p.chunk * (dpad - d); idx += nthreads) {
         const int t = idx / (dpad - d), i = d + idx - t * (dpad - d);
@@ -235,15 +235,14 @@ __global__ void decay_scan_kernel(const DecayScanParams p) {
         }
         __syncthreads();                                  // the chunk has been read by everyone
     }
-    // ---- the state back, the same way ----------------------------------------------------------------------------------------------
+    // ---- the state back (entries of a column's last piece beyond d stay zero: their k, q and decay are) ---------------------------
+    if (col_ok) {
 #pragma unroll
-    for (int e = 0; e < EPL; e++) {
-        const int i = 4 * ((e >> 2) * L + lane) + (e & 3);
-        if (i < d) smem[i * kDsCols + col] = s[e];
+        for (int g = 0; g < EPL / 4; g++) {
+            const int i4 = 4 * (g * L + lane);
+            if (i4 < d4) *reinterpret_cast<float4 *>(st + i4) = make_float4(s[4 * g + 0], s[4 * g + 1], s[4 * g + 2], s[4 * g + 3]);
+        }
     }
-    __syncthreads();
-    for (int idx = tid; idx < d * kDsCols / 4; idx += nthreads)
-        reinterpret_cast<float4 *>(st)[idx] = reinterpret_cast<const float4 *>(smem)[idx];
 }
 
 }  // namespace iian
@@ -260,12 +259,12 @@ static int g_decay_scan_per_lane = 0;          // 0: chosen per launch; 8 or 16:
 IIAN_API void iian_decay_scan_set_entries_per_lane(int per_lane) { g_decay_scan_per_lane = per_lane <= 0 ? 0 : per_lane <= 8 ? 8 : 16; }
 IIAN_API int iian_decay_scan_lanes(int d) { return decay_scan_lanes(d, 16); }
 
-// floats of one (slot, head) of the state: blocks of 16 columns, each [d, 16]
-IIAN_API long long iian_decay_scan_state_floats(int d, int dv) { return (long long) ((dv + kDsCols - 1) / kDsCols) * d * kDsCols; }
+// floats of one (slot, head) of the state: blocks of 16 columns of d4 = round_up(d, 4) floats each
+IIAN_API long long iian_decay_scan_state_floats(int d, int dv) { return (long long) ((dv + kDsCols - 1) / kDsCols) * kDsCols * ((d + 3) & ~3); }
 
 // proj: A rows [.. q (H * d) .. k (H * d) .. v (H * dv) ..] at the given column offsets, row stride ld.
 // head_decay: f32 [H] (one constant decay per head) or null, then z: f32 rows of H * d (row stride ld_z), z_bias f32 [H * d]
-// or null, inv_tau.  state: f32 [num_slots, H, ceil(dv / 16), d, 16].  out: f32 [n, H * dv].  max_q_len: the longest portion of
+// or null, inv_tau.  state: f32 [num_slots, H, ceil(dv / 16), 16, round_up(d, 4)].  out: f32 [n, H * dv].  max_q_len: the longest portion of
 // the step (sizes the chunks; 0: unknown).
 IIAN_API int iian_decay_scan(const void * proj, long long ld, int q_off, int k_off, int v_off, int act, float q_scale,
                              const float * head_decay, const float * z, long long ld_z, const float * z_bias, float inv_tau,
@@ -293,8 +292,7 @@ IIAN_API int iian_decay_scan(const void * proj, long long ld, int q_off, int k_o
     int chunk = d <= 128 ? 16 : d <= 256 ? 8 : 4;
     if (max_q_len > 0 && max_q_len < chunk) chunk = max_q_len;
     p.chunk = chunk;
-    const size_t rows = ((size_t) chunk * p.dpad * (head_decay == nullptr ? 3 : 2) + (size_t) chunk * kDsCols) * sizeof(float);
-    const size_t smem = rows > (size_t) d * kDsCols * sizeof(float) ? rows : (size_t) d * kDsCols * sizeof(float);
+    const size_t smem = ((size_t) chunk * p.dpad * (head_decay == nullptr ? 3 : 2) + (size_t) chunk * kDsCols) * sizeof(float);
     dim3 grid((dv + kDsCols - 1) / kDsCols, H, S), block(kDsCols * p.L);
     const bool vec = chunk * (d / 8) <= 2 * (int) block.x && chunk * kDsCols <= 4 * (int) block.x && act_dtype == IIAN_BF16 && d % 8 == 0 && ld % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && ((uintptr_t) proj & 15) == 0 &&
                      (head_decay != nullptr || (ld_z % 4 == 0 && ((uintptr_t) z & 15) == 0));

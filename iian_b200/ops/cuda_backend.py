@@ -1660,7 +1660,7 @@ class CudaKernels:
                    q_scale: float, head_decay: Optional[torch.Tensor] = None, z: Optional[torch.Tensor] = None,
                    z_bias: Optional[torch.Tensor] = None, tau: float = 1.0, max_q_len: int = 0) -> None:
         """Walk every sequence's tokens of this step through ``S <- diag(a) S + k v^T``, ``o = S^T q`` from and into ``state``
-        [slots, heads, ceil(v_dim / 16), dim, 16] (float32, blocks of 16 columns).  ``proj`` rows hold q, k, v at the given column offsets (``activation`` ``silu``:
+        [slots, heads, ceil(v_dim / 16), 16, dim rounded up to 4] (float32, column by column in blocks of 16).  ``proj`` rows hold q, k, v at the given column offsets (``activation`` ``silu``:
         all three pass it first); q is multiplied by ``q_scale``.  The decay is ``head_decay`` [heads] (one constant per head)
         or, per token and key channel, ``sigmoid(z + z_bias)^(1 / tau)`` with ``z`` float32 [N, heads * dim] (may be a column
         slice).  ``out`` float32 [N, heads * v_dim]."""
@@ -1668,7 +1668,7 @@ class CudaKernels:
         pp, ld = self._rows(proj, "projections")
         zp, ld_z = self._rows(z, "decay pre-activations")
         s = cu_q.numel() - 1
-        if out.shape != (n, num_heads * v_dim) or state_slots.numel() != s or state.dim() != 5 or state.shape[1:] != (num_heads, -(-v_dim // 16), dim, 16) \
+        if out.shape != (n, num_heads * v_dim) or state_slots.numel() != s or state.dim() != 5 or state.shape[1:] != (num_heads, -(-v_dim // 16), 16, (dim + 3) // 4 * 4) \
                 or (head_decay is None) == (z is None) or (head_decay is not None and head_decay.numel() != num_heads) \
                 or (z is not None and (z.shape != (n, num_heads * dim) or z.dtype != torch.float32)) \
                 or (z_bias is not None and z_bias.numel() != num_heads * dim) or activation not in (None, "silu"):

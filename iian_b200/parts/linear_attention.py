@@ -13,7 +13,7 @@ The read-out passes an RMS norm -- ``norm = "all"``: over all heads together wit
 ``norm = "head"``: every head over its own v_dim entries with ONE weight vector [v_dim] shared by the heads -- is multiplied
 by ``gate_act(Wg h)`` (``sigmoid`` | ``silu``), and projected by ``Wo``.
 
-The state (float32, stored in blocks of 16 columns: [heads, blocks, dim, 16]) lives in the request's state slot and is carried
+The state (float32, stored column by column in blocks of 16 columns: [heads, blocks, 16, dim rounded up to 4]) lives in the request's state slot and is carried
 from step to step; a step walks the tokens it brings in order.  ``Wq | Wk | Wv | Wg`` are one product in the activation dtype (``input_rows``); the decay's first matrix is a small
 product of its own, its second one a product with float32 output; decays, the state and the recurrence are float32 in both
 dtypes (``csrc/decay_scan.cu``).
@@ -100,11 +100,11 @@ class DecayLinearAttention(Mixer):
     def input_rows(self) -> torch.Tensor:
         return self.w_in
 
-    STATE_COLUMNS = 16          # the scan kernel keeps the state in blocks of that many columns (csrc/decay_scan.cu)
+    STATE_COLUMNS = 16          # the scan kernel keeps the state in blocks of that many contiguous columns (csrc/decay_scan.cu)
 
     def cache_need(self) -> StateNeed:
         blocks = -(-self.vdim // self.STATE_COLUMNS)
-        return StateNeed((self.nh, blocks, self.dim, self.STATE_COLUMNS), torch.float32)
+        return StateNeed((self.nh, blocks, self.STATE_COLUMNS, (self.dim + 3) // 4 * 4), torch.float32)
 
     def kernel_libraries(self):
         return ("decay_scan", "stream_ops", "gemm_simt")

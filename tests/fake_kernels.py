@@ -530,7 +530,7 @@ class FakeKernels:
             if slot < 0:
                 out[t0:t1] = 0
                 continue
-            S = state[slot].permute(0, 2, 1, 3).reshape(H, D, -1)[:, :, :V].clone()       # blocks of 16 columns -> [H, D, V]
+            S = state[slot].reshape(H, -1, state.shape[-1])[:, :V, :D].transpose(1, 2).clone()     # columns in blocks of 16 -> [H, D, V]
             for t in range(t0, t1):
                 q = act(proj[t, q_off:q_off + H * D].float()).view(H, D) * q_scale
                 k = act(proj[t, k_off:k_off + H * D].float()).view(H, D)
@@ -542,10 +542,9 @@ class FakeKernels:
                     a = torch.exp(torch.nn.functional.logsigmoid(zz) / tau).view(H, D)
                 S = a[:, :, None] * S + k[:, :, None] * v[:, None, :]
                 out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(H * V)
-            blocks = state.shape[2]
-            full = torch.zeros(H, D, blocks * 16)
-            full[:, :, :V] = S
-            state[slot] = full.view(H, D, blocks, 16).permute(0, 2, 1, 3)
+            full = torch.zeros(H, state.shape[2] * 16, state.shape[-1])
+            full[:, :V, :D] = S.transpose(1, 2)
+            state[slot] = full.view(state.shape[1:])
 
     def moe_route_softmax(self, logits, bias, top, ids, weights):
         z = logits.float() + (bias if bias is not None else 0.0)

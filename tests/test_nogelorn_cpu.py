@@ -155,8 +155,8 @@ def test_tensor_names_and_cache_needs(tmp_path):
     assert sorted(needs) == sorted([0, 2, 4, 5] + [m for p in pair for m in p])
     assert needs[pair[0][0]] == needs[pair[1][0]] == KVNeed(2, 16, 24, 24)             # a plain window gives pages back
     assert needs[2] == needs[4] == KVNeed(4, 24, None, 16)                             # kept first keys: every page stays
-    assert needs[pair[0][1]] == StateNeed((3, 1, 24, 16), torch.float32)               # blocks of 16 columns: 16 -> 1, 40 -> 3
-    assert needs[0] == StateNeed((3, 3, 24, 16), torch.float32)
+    assert needs[pair[0][1]] == StateNeed((3, 1, 16, 24), torch.float32)               # blocks of 16 columns: 16 -> 1, 40 -> 3
+    assert needs[0] == StateNeed((3, 3, 16, 24), torch.float32)
 
 
 def test_the_decay_rank_comes_from_the_tensor_when_the_file_is_silent(tmp_path):

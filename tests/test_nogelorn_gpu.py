@@ -285,7 +285,7 @@ def test_decayed_scan_cut_into_steps_with_slots_used_again(dtype, H, d, dv, per_
     tau, q_scale, act = 3.0, d ** -0.5, not per_channel
     want = [_plain_scan(p.double()[:, 4:], H, d, dv, act, q_scale, None if per_channel else head_decay.double(), z.double(), bias.double(), tau)[0]
             for p, z in zip(projs, zs)]
-    state = torch.zeros(4, H, -(-dv // 16), d, 16, device=DEV)
+    state = torch.zeros(4, H, -(-dv // 16), 16, (d + 3) // 4 * 4, device=DEV)
     slots = [2, 0, 3]
     fed = [0, 0, 0]
     got = [torch.zeros(n, H * dv) for n in lengths]
